@@ -1,0 +1,88 @@
+// Shared helpers for the sm_100a kernels: element types, 32-bit loads of either storage type,
+// warp/block reductions and the error convention of the exported entry points.
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes and a stream, checks
+// what it cannot handle and returns 0 on success or a negative code after recording a message
+// that `cuinfer_last_error()` hands to the caller.  Nothing here allocates.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace cib {
+
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+constexpr int kWarp = 32;
+
+// ---- error reporting -------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+
+#define CIB_REQUIRE(cond, ...)            \
+    do {                                  \
+        if (!(cond)) {                    \
+            ::cib::set_error(__VA_ARGS__); \
+            return -1;                    \
+        }                                 \
+    } while (0)
+
+#define CIB_LAUNCH_CHECK(name)                                                     \
+    do {                                                                           \
+        cudaError_t e__ = cudaGetLastError();                                      \
+        if (e__ != cudaSuccess) {                                                  \
+            ::cib::set_error("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+            return -2;                                                             \
+        }                                                                          \
+    } while (0)
+
+// ---- typed access ------------------------------------------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// A vector that is stored either in 32 bits or in bfloat16, chosen at run time (norm gains keep
+// the precision they were stored in, whatever the engine's dtype).
+struct AnyVec {
+    const void* ptr;
+    int is_bf16;
+    __device__ __forceinline__ float operator[](int i) const {
+        return is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ptr)[i])
+                       : reinterpret_cast<const float*>(ptr)[i];
+    }
+};
+
+// ---- reductions ----------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+}  // namespace cib

@@ -1,0 +1,291 @@
+"""The step function: run the tokens a batch brings, from the cache, and return logits at the wanted places.
+
+The reference's ``ModelRunner::run_model`` (csrc/executor/model_runner.cpp:60-92) packs the scheduled
+requests into flat arrays (csrc/executor/batch_buffer.cpp:57-168: token ids, positions =
+``position_offset + j``, slot mapping = ``table[pos / bs] * bs + pos % bs``, ``query_start_loc`` prefix
+sums, ``seq_lens = offset + n``, block-table rows, index of each request's last token), copies them to
+the device in one transfer from pinned memory, runs the model and samples.  Here the step stops at the
+logits (32-bit, any number of wanted positions per entry); sampling is a separate call above it.
+
+A batch is a list of :class:`StepEntry`: a request id, its next tokens (a whole prompt, a portion of
+one, or a single decoded token) and the positions among them whose logits are wanted.  Pages for the
+new tokens must have been allocated in the cache manager before the step (the scheduler or the replay
+tool does that); the step records the stored tokens afterwards.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, CacheStorage, group_runs, page_bytes
+from ..config import EngineConfig, load_model_config
+from ..parts import DecoderModel, GroupView, PagedKV, StepContext
+from ..weights import WeightStore
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class StepError(RuntimeError):
+    """A batch the step function cannot run; the message says which entry and why."""
+
+
+@dataclass
+class StepEntry:
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)   # indices into ``tokens`` whose logits are wanted
+
+
+class _PinnedRing:
+    """A few pinned staging buffers used in turn; a buffer is reused only after its copy has finished."""
+
+    def __init__(self, count: int = 3) -> None:
+        self._bufs: List[Optional[torch.Tensor]] = [None] * count
+        self._events: List[Optional[torch.cuda.Event]] = [None] * count
+        self._next = 0
+
+    def get(self, num_ints: int) -> tuple[torch.Tensor, int]:
+        i = self._next
+        self._next = (self._next + 1) % len(self._bufs)
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        buf = self._bufs[i]
+        if buf is None or buf.numel() < num_ints:
+            size = max(4096, 1 << (num_ints - 1).bit_length())
+            buf = torch.empty(size, dtype=torch.int32, pin_memory=True)
+            self._bufs[i] = buf
+        return buf, i
+
+    def mark(self, i: int) -> None:
+        ev = self._events[i]
+        if ev is None:
+            ev = torch.cuda.Event()
+            self._events[i] = ev
+        ev.record()
+
+
+class ModelRunner:
+    def __init__(self, model_dir: str, config: EngineConfig, *, num_blocks: Optional[int] = None) -> None:
+        if not torch.cuda.is_available():
+            raise RuntimeError("cuinfer_b200 runs on a CUDA device only; none is visible")
+        self.config = config
+        self.device = torch.device(config.device)
+        torch.cuda.set_device(self.device)
+        self.dtype = _DTYPES[config.dtype]
+        self.architecture, self.model_config = load_model_config(model_dir)
+        self.spec = self.architecture.spec(self.model_config)
+        self.model = DecoderModel(self.spec, self.dtype)
+        store = WeightStore(model_dir, self.dtype, self.device)
+        try:
+            self.model.load(store)
+        finally:
+            store.close()
+        self.vocab_size = self.spec.vocab_size
+        self.max_model_len = self.spec.max_positions
+        self.page_size = config.block_size
+
+        needs = self.model.cache_needs()
+        self.groups = group_runs(needs)
+        pages = num_blocks if num_blocks is not None else config.num_blocks
+        if pages is None:
+            pages = self._pages_from_memory()
+        self.num_pages = int(pages)
+        self.manager = CacheManager(self.groups, self.page_size, self.num_pages, config.max_num_seqs)
+        self.storage = CacheStorage(self.groups, self.page_size, [self.num_pages] * len(self.groups),
+                                    self.model.state_needs(), config.max_num_seqs, self.dtype, self.device)
+        # which cache every run uses (its own, or an earlier run's)
+        self._run_cache: Dict[int, tuple[int, bool]] = {}
+        for run, _layer in self.model.runs():
+            src = self.model.cache_source.get(run, run)
+            if src in self.storage.run_cache:
+                self._run_cache[run] = (src, src == run)
+        self._ring = _PinnedRing()
+        self._arena: Optional[torch.Tensor] = None
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ---- sizing ------------------------------------------------------------------------------------
+    def page_bytes(self) -> int:
+        return sum(page_bytes(g, self.page_size, self.dtype) for g in self.groups)
+
+    def _pages_from_memory(self) -> int:
+        """Pages that fit in ``gpu_memory_utilization`` of the device after the weights
+        (csrc/executor/model_runner.cpp:154-163, csrc/engine/engine_core.cpp:111-128)."""
+        free, total = torch.cuda.mem_get_info(self.device)
+        used = total - free
+        budget = int(total * self.config.gpu_memory_utilization) - used
+        # room for a step's activations: qkv/gate_up/logits rows of a full token budget
+        budget -= self._activation_bytes()
+        per_page = max(1, self.page_bytes())
+        pages = budget // per_page
+        need = (self.max_model_len + self.page_size - 1) // self.page_size
+        if pages < need:
+            raise RuntimeError(
+                f"the cache pool would hold {max(pages, 0)} pages of {self.page_size} tokens, fewer than one request of "
+                f"max_model_len={self.max_model_len} needs ({need}); raise gpu_memory_utilization or give num_blocks")
+        return int(pages)
+
+    def _activation_bytes(self) -> int:
+        t = self.config.max_num_scheduled_tokens
+        widest = 0
+        for layer in self.spec.layers:
+            inter = layer.feed_forward.get("intermediate_size", 0) or 0
+            heads = (layer.mixer.get("num_heads", 0) or 0) + 2 * (layer.mixer.get("num_kv_heads", 0) or 0)
+            widest = max(widest, 3 * inter, 2 * heads * (layer.mixer.get("head_dim", 0) or 0))
+        width = 2 if self.dtype == torch.bfloat16 else 4
+        return t * (widest * width + 3 * self.spec.hidden_size * 4) + self.config.max_num_seqs * self.vocab_size * 8
+
+    # ---- requests ------------------------------------------------------------------------------------
+    def reserve(self, request_id: Hashable, num_new_tokens: int) -> bool:
+        """Admit the request if it is new and allocate pages for ``num_new_tokens`` more tokens.
+        False (and nothing changed) when slots or pages are short."""
+        fresh = request_id not in self.manager
+        if fresh and self.manager.admit(request_id) is None:
+            return False
+        if not self.manager.allocate(request_id, num_new_tokens):
+            if fresh:
+                self.manager.release(request_id)
+            return False
+        return True
+
+    def release(self, request_id: Hashable) -> None:
+        if request_id in self.manager:
+            self.manager.release(request_id)
+
+    # ---- one step ----------------------------------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if len(entries) > self.config.max_num_seqs:
+            raise StepError(f"{len(entries)} requests in one step exceed max_num_seqs={self.config.max_num_seqs}")
+        seen = set()
+        total = 0
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.request_id!r} brings no tokens")
+            if e.request_id not in self.manager:
+                raise StepError(f"request {e.request_id!r} has no pages; reserve() it before the step")
+            have = self.manager.num_tokens(e.request_id)
+            if have + n > self.max_model_len:
+                raise StepError(f"request {e.request_id!r} would reach {have + n} tokens, beyond max_model_len={self.max_model_len}")
+            if any(p > 0 for p in self.manager.pages_needed(e.request_id, n)):
+                raise StepError(f"request {e.request_id!r} lacks pages for {n} more tokens; reserve() them before the step")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.request_id!r}: wanted index {w} is outside its {n} tokens")
+            for tok in e.tokens:
+                if not 0 <= tok < self.vocab_size:
+                    raise StepError(f"request {e.request_id!r}: token id {tok} is outside the vocabulary of {self.vocab_size}")
+            total += n
+        if total > self.config.max_num_scheduled_tokens:
+            raise StepError(f"{total} tokens in one step exceed max_num_scheduled_tokens={self.config.max_num_scheduled_tokens}")
+
+    def build_context(self, entries: Sequence[StepEntry], table_stride: Optional[int] = None):
+        """Pack the batch, copy it to the device and return ``(StepContext, logits_indices tensor)``."""
+        mgr = self.manager
+        R = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        starts = [mgr.num_tokens(e.request_id) for e in entries]
+        T = sum(lens)
+        S = sum(len(e.want) for e in entries)
+        G = len(self.groups)
+        P = table_stride or max(1, max(len(mgr.block_table(e.request_id, g)) for e in entries for g in range(G))) if G else 1
+        total = 3 * T + (R + 1) + 2 * R + S + G * (T + R * P)
+        pinned, ring_idx = self._ring.get(total)
+        host = pinned.numpy()
+        off = 0
+
+        def take(n: int) -> tuple[np.ndarray, int]:
+            nonlocal off
+            view = host[off:off + n]
+            begin = off
+            off += n
+            return view, begin
+
+        tok, o_tok = take(T)
+        pos, o_pos = take(T)
+        treq, o_treq = take(T)
+        qsl, o_qsl = take(R + 1)
+        sl, o_sl = take(R)
+        slots, o_slots = take(R)
+        want, o_want = take(S)
+        qsl[0] = 0
+        t0 = 0
+        w0 = 0
+        for r, e in enumerate(entries):
+            n = lens[r]
+            tok[t0:t0 + n] = np.asarray(e.tokens, dtype=np.int32)
+            pos[t0:t0 + n] = np.arange(starts[r], starts[r] + n, dtype=np.int32)
+            treq[t0:t0 + n] = r
+            qsl[r + 1] = t0 + n
+            sl[r] = starts[r] + n
+            slots[r] = mgr.slot(e.request_id)
+            for w in e.want:
+                want[w0] = t0 + w
+                w0 += 1
+            t0 += n
+        group_offsets = []
+        for g in range(G):
+            sm, o_sm = take(T)
+            bt, o_bt = take(R * P)
+            bt[:] = -1
+            t0 = 0
+            for r, e in enumerate(entries):
+                table = mgr.block_table(e.request_id, g)
+                if len(table) > P:
+                    raise StepError(f"request {e.request_id!r} holds {len(table)} pages, more than the table stride {P}")
+                row = np.asarray(table, dtype=np.int32)
+                bt[r * P:r * P + len(table)] = row
+                p = np.arange(starts[r], starts[r] + lens[r], dtype=np.int32)
+                pages = row[p // self.page_size]
+                if (pages < 0).any():
+                    raise StepError(f"request {e.request_id!r}: a new token has no page in group {g}")
+                sm[t0:t0 + lens[r]] = pages * self.page_size + p % self.page_size
+                t0 += lens[r]
+            group_offsets.append((o_sm, o_bt))
+
+        if self._arena is None or self._arena.numel() < total:
+            self._arena = torch.empty(max(4096, 1 << (total - 1).bit_length()), dtype=torch.int32, device=self.device)
+        dev = self._arena[:total]
+        dev.copy_(pinned[:total], non_blocking=True)
+        self._ring.mark(ring_idx)
+
+        groups = {}
+        for g, (o_sm, o_bt) in enumerate(group_offsets):
+            groups[g] = GroupView(self.page_size, dev[o_bt:o_bt + R * P].view(R, P), dev[o_sm:o_sm + T])
+        ctx = StepContext(
+            num_tokens=T, num_requests=R,
+            token_ids=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T], token_request=dev[o_treq:o_treq + T],
+            query_start_loc=dev[o_qsl:o_qsl + R + 1], seq_lens=dev[o_sl:o_sl + R], state_slots=dev[o_slots:o_slots + R],
+            query_start_loc_host=[int(v) for v in qsl], seq_lens_host=[int(v) for v in sl],
+            state_slots_host=[int(v) for v in slots],
+            max_query_len=max(lens), max_seq_len=max(int(v) for v in sl), groups=groups,
+            decode_only=all(n == 1 for n in lens),
+        )
+        for run, (src, writes) in self._run_cache.items():
+            ctx.kv[run] = PagedKV(self.storage.run_cache[src], groups[self.storage.run_group[src]], writes)
+        ctx.state = self.storage.state
+        return ctx, dev[o_want:o_want + S]
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the batch and return float32 logits ``[sum(len(e.want)), vocab]`` in entry order (device tensor)."""
+        self._validate(entries)
+        self.storage.zero_slots(self.manager.take_newly_admitted())
+        ctx, want = self.build_context(entries)
+        stream = self.model.forward(ctx)
+        if want.numel():
+            logits = self.model.logits(stream, want)
+        else:
+            logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        for e in entries:
+            self.manager.commit(e.request_id, len(e.tokens))
+        self.steps_run += 1
+        self.tokens_run += ctx.num_tokens
+        return logits

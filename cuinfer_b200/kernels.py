@@ -1,0 +1,259 @@
+"""Python face of the CUDA kernels: one thin function per exported entry point.
+
+The shared library is compiled from ``cuinfer_b200/csrc`` on first use (see ``csrc/build.py``) and
+loaded with ctypes.  Every function takes torch CUDA tensors, checks dtypes, shapes and contiguity,
+and launches on torch's current stream, so that calls are ordered with torch's own work and are
+recorded when a CUDA graph is being captured.  There is no CPU or library fallback: if the library
+cannot be built or loaded, or a tensor is not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+_lib_handle: Optional[ctypes.CDLL] = None
+_lib_lock = threading.Lock()
+
+# Number of kernel launches issued through this module (each wrapper call launches one kernel unless
+# it says otherwise).  The benchmark reads it.
+launch_count = 0
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library; built first if it is missing or stale."""
+    global _lib_handle
+    if _lib_handle is not None:
+        return _lib_handle
+    with _lib_lock:
+        if _lib_handle is not None:
+            return _lib_handle
+        try:
+            path = _build.build(verbose=True)
+            lib = ctypes.CDLL(path)
+        except Exception as exc:  # noqa: BLE001 - anything here means the product path cannot run
+            raise KernelError(
+                "the CUDA kernel library of cuinfer_b200 is not available, and there is no fallback: "
+                f"{type(exc).__name__}: {exc}"
+            ) from exc
+        lib.cib_last_error.restype = ctypes.c_char_p
+        _declare(lib)
+        _lib_handle = lib
+        return lib
+
+
+def library_path() -> str:
+    library()
+    return _build.library_path()
+
+
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    sig = {
+        "cib_embedding_gather": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+        "cib_add_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
+        "cib_gather_rows": [_P, _P, _I, _P, _P, _I, _I, _I, _P],
+        "cib_silu_mul": [_P, _P, _I, _I, _I, _P],
+        "cib_qk_norm_rope_kv_write": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+        "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
+        "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
+    }
+    for name, argtypes in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = _I
+
+
+def _check(rc: int, name: str) -> None:
+    if rc != 0:
+        msg = library().cib_last_error()
+        raise KernelError(f"{name} failed ({rc}): {msg.decode() if msg else 'no message'}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _cuda(t: torch.Tensor, what: str, dtype: torch.dtype | None = None, contiguous: bool = True) -> int:
+    if not t.is_cuda:
+        raise KernelError(f"{what} must be a CUDA tensor; cuinfer_b200 has no CPU path")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+    return t.data_ptr()
+
+
+def _count() -> None:
+    global launch_count
+    launch_count += 1
+
+
+# ---- row-wise kernels ----------------------------------------------------------------------------
+
+def embedding_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, bad_flag: torch.Tensor | None = None) -> None:
+    """out[t] = table[ids[t]] as float32 rows."""
+    T = ids.numel()
+    V, H = table.shape
+    if out.shape != (T, H):
+        raise KernelError(f"embedding_gather: out must be [{T}, {H}], got {list(out.shape)}")
+    rc = library().cib_embedding_gather(
+        _cuda(ids, "ids", torch.int32), _cuda(table, "table"), _code(table, "table"), _cuda(out, "out", torch.float32),
+        T, H, V, _cuda(bad_flag, "bad_flag", torch.int32) if bad_flag is not None else None, _stream())
+    _check(rc, "embedding_gather")
+    _count()
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor | None, eps: float,
+                out: torch.Tensor | None) -> None:
+    """residual += delta (if given); out = rmsnorm(residual) * weight (if out given)."""
+    rows, H = residual.shape
+    if delta is not None and delta.shape != residual.shape:
+        raise KernelError(f"add_rmsnorm: delta {list(delta.shape)} does not match residual {list(residual.shape)}")
+    if out is not None:
+        if out.shape != residual.shape:
+            raise KernelError(f"add_rmsnorm: out {list(out.shape)} does not match residual {list(residual.shape)}")
+        if weight is None or weight.numel() != H:
+            raise KernelError(f"add_rmsnorm: weight must have {H} elements")
+    rc = library().cib_add_rmsnorm(
+        _cuda(residual, "residual", torch.float32),
+        _cuda(delta, "delta") if delta is not None else None, _code(delta, "delta") if delta is not None else 0,
+        _cuda(weight, "weight") if weight is not None else None, _code(weight, "weight") if weight is not None else 0,
+        float(eps), _cuda(out, "out") if out is not None else None, _code(out, "out") if out is not None else 0,
+        rows, H, _stream())
+    _check(rc, "add_rmsnorm")
+    _count()
+
+
+def gather_rows(residual: torch.Tensor, delta: torch.Tensor | None, indices: torch.Tensor, out: torch.Tensor) -> None:
+    """out[s] = residual[indices[s]] (+ delta[indices[s]]), float32."""
+    rows, H = residual.shape
+    S = indices.numel()
+    if out.shape != (S, H):
+        raise KernelError(f"gather_rows: out must be [{S}, {H}]")
+    rc = library().cib_gather_rows(
+        _cuda(residual, "residual", torch.float32),
+        _cuda(delta, "delta") if delta is not None else None, _code(delta, "delta") if delta is not None else 0,
+        _cuda(indices, "indices", torch.int32), _cuda(out, "out", torch.float32), S, H, rows, _stream())
+    _check(rc, "gather_rows")
+    _count()
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]."""
+    rows, two_i = gate_up.shape
+    inter = two_i // 2
+    if two_i != 2 * inter or out.shape != (rows, inter) or out.dtype != gate_up.dtype:
+        raise KernelError(f"silu_mul: gate_up {list(gate_up.shape)} / out {list(out.shape)} do not fit")
+    rc = library().cib_silu_mul(_cuda(gate_up, "gate_up"), _cuda(out, "out"), _code(gate_up, "gate_up"), rows, inter, _stream())
+    _check(rc, "silu_mul")
+    _count()
+
+
+# ---- attention -------------------------------------------------------------------------------------
+
+def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor | None,
+                          q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
+                          rope_table: torch.Tensor | None, rotary_dim: int, cache: torch.Tensor | None,
+                          num_q_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """Per-head RMSNorm (if weights are given) and rotary encoding (if a table is given) of the query and
+    key heads of the packed ``qkv`` rows; queries are rewritten in place, keys and values are written to
+    ``cache[page, 0|1, kv head, slot, :]`` (if a cache is given)."""
+    T, stride = qkv.shape
+    has_norm = q_weight is not None
+    if has_norm and (k_weight is None or q_weight.dtype != k_weight.dtype):
+        raise KernelError("qk_norm_rope: q and k norm weights must both be given, in one dtype")
+    write_cache = cache is not None
+    if write_cache:
+        if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+            raise KernelError(f"qk_norm_rope: cache must be [pages, 2, {num_kv_heads}, page_size, {head_dim}], got {list(cache.shape)}")
+        if cache.dtype != qkv.dtype:
+            raise KernelError("qk_norm_rope: cache and qkv must have one dtype")
+        if slot_mapping is None:
+            raise KernelError("qk_norm_rope: a cache write needs slot_mapping")
+    if rope_table is not None and (rope_table.dim() != 3 or rope_table.shape[1] * 2 != rotary_dim or rope_table.shape[2] != 2):
+        raise KernelError(f"qk_norm_rope: rope table must be [positions, {rotary_dim // 2}, 2], got {list(rope_table.shape)}")
+    rc = library().cib_qk_norm_rope_kv_write(
+        _cuda(qkv, "qkv"), _code(qkv, "qkv"), stride, _cuda(positions, "positions", torch.int32),
+        _cuda(slot_mapping, "slot_mapping", torch.int32) if slot_mapping is not None else None,
+        _cuda(q_weight, "q_weight") if has_norm else None, _cuda(k_weight, "k_weight") if has_norm else None,
+        _code(q_weight, "q_weight") if has_norm else 0, 1 if has_norm else 0, float(eps),
+        _cuda(rope_table, "rope_table", torch.float32) if rope_table is not None else None,
+        rotary_dim if rope_table is not None else 0, rope_table.shape[0] if rope_table is not None else 0,
+        _cuda(cache, "cache") if write_cache else None, cache.shape[0] if write_cache else 0,
+        cache.shape[3] if write_cache else 0, T, num_q_heads, num_kv_heads, head_dim, 1 if write_cache else 0, _stream())
+    _check(rc, "qk_norm_rope_kv_write")
+    _count()
+
+
+def paged_attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                            query_start_loc: torch.Tensor, seq_lens: torch.Tensor, token_request: torch.Tensor,
+                            num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """Causal attention of the packed query rows ``q[:, :nq*d]`` over the paged cache; out[T, nq*d]."""
+    T = q.shape[0]
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("paged_attention: q and out rows must be dense")
+    if out.shape != (T, num_q_heads * head_dim) or out.dtype != q.dtype or cache.dtype != q.dtype:
+        raise KernelError("paged_attention: out/cache do not fit q")
+    rc = library().cib_paged_attention_generic(
+        _cuda(q, "q", contiguous=False), _code(q, "q"), q.stride(0), _cuda(out, "out", contiguous=False), out.stride(0),
+        _cuda(cache, "cache"), cache.shape[0], cache.shape[3],
+        _cuda(block_table, "block_table", torch.int32), block_table.stride(0),
+        _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32),
+        _cuda(token_request, "token_request", torch.int32), T, num_q_heads, num_kv_heads, head_dim, float(scale),
+        int(window), _stream())
+    _check(rc, "paged_attention_generic")
+    _count()
+
+
+# ---- matrix product ----------------------------------------------------------------------------------
+
+def gemm_generic(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T with 32-bit FMA accumulation, any sizes."""
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2 or out.shape != (M, N) or a.dtype != w.dtype:
+        raise KernelError(f"gemm: a {list(a.shape)} {a.dtype}, w {list(w.shape)} {w.dtype}, out {list(out.shape)} do not fit")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm: rows must be dense")
+    rc = library().cib_gemm_generic(
+        _cuda(a, "a", contiguous=False), a.stride(0), _cuda(w, "w", contiguous=False), w.stride(0), _code(a, "a"),
+        _cuda(out, "out", contiguous=False), out.stride(0), _code(out, "out"), M, N, K, _stream())
+    _check(rc, "gemm_generic")
+    _count()
+
+
+# ---- sampling ----------------------------------------------------------------------------------------
+
+def sample(logits: torch.Tensor, params: torch.Tensor, out_ids: torch.Tensor) -> None:
+    """out_ids[s] = token drawn from logits[s]; params[s] = (temperature, top_k as int bits, top_p, u)."""
+    S, V = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("sample: logits rows must be dense")
+    if params.numel() * params.element_size() < S * 16:
+        raise KernelError("sample: params must hold 16 bytes per row")
+    rc = library().cib_sample(_cuda(logits, "logits", torch.float32, contiguous=False), logits.stride(0), S, V,
+                              _cuda(params, "params"), _cuda(out_ids, "out_ids", torch.int32), _stream())
+    _check(rc, "sample")
+    _count()

@@ -1,0 +1,18 @@
+"""Choice of the paged-attention kernel for a step.
+
+float32 always runs the all-sizes kernel.  bfloat16 runs the tensor-core kernels where they take the
+head size and falls back to the all-sizes kernel otherwise; a size no kernel takes raises there.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .context import PagedKV, StepContext
+
+
+def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepContext, num_heads: int,
+                    num_kv_heads: int, head_dim: int, scale: float, window: int) -> None:
+    kernels.paged_attention_generic(
+        qkv, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens, ctx.token_request,
+        num_heads, num_kv_heads, head_dim, scale, window)

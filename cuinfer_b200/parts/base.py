@@ -1,0 +1,99 @@
+"""Interfaces of the parts a layer is made of.
+
+A part is built from its :class:`PartSpec` plus the sizes of its surroundings (hidden size, engine
+dtype, checkpoint prefix).  It announces the tensors it expects (``tensors``), takes them from the
+weight store (``load``), says what it keeps between steps (``cache_need`` / ``state_need``) and
+computes (``forward``).  No part knows which model it sits in.
+
+Interfaces
+----------
+Norm            ``add_norm(stream) -> normed [T, H]`` folds the pending delta into the 32-bit residual and
+                norms it; ``norm_rows(x32) -> [S, H]`` norms given 32-bit rows.
+PositionEncoding ``table() -> float32 [positions, rotary_dim/2, 2]`` or None, ``rotary_dim``.
+Mixer           ``forward(x [T, H], ctx, run) -> [T, H]``; ``cache_need()``, ``state_need()``.
+FeedForward     ``forward(x [T, H], ctx) -> [T, H]``.
+Block           ``forward(stream, ctx, run)``: arranges norms, mixer and feed-forward around the residual.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .context import StepContext
+from .spec import PagedCacheNeed, PartSpec, StateNeed, TensorSpec
+
+
+class ResidualStream:
+    """The 32-bit residual rows of a step and a delta that has not been added yet.
+
+    Keeping the last sub-layer's output pending lets the next norm do the add, the store of the new
+    residual and the normalisation in one pass.
+    """
+
+    __slots__ = ("residual", "pending")
+
+    def __init__(self, residual: torch.Tensor, pending: Optional[torch.Tensor] = None) -> None:
+        self.residual = residual
+        self.pending = pending
+
+
+class Part:
+    def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
+        self.spec = spec
+        self.hidden_size = hidden_size
+        self.prefix = prefix
+        self.dtype = dtype
+
+    def tensors(self) -> List[TensorSpec]:
+        return []
+
+    def load(self, store) -> None:  # store: cuinfer_b200.weights.WeightStore
+        pass
+
+
+class Norm(Part):
+    def add_norm(self, stream: ResidualStream) -> torch.Tensor:
+        raise NotImplementedError
+
+    def norm_rows(self, rows: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    rotary_dim: int = 0
+
+    def table(self) -> Optional[torch.Tensor]:
+        return None
+
+
+class Mixer(Part):
+    def cache_need(self) -> Optional[PagedCacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, run: int) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """An arrangement of norms, a mixer and a feed-forward around the residual stream."""
+
+    def __init__(self, spec: PartSpec, *, mixer: Mixer, feed_forward: FeedForward, make_norm, prefix: str) -> None:
+        self.spec = spec
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.prefix = prefix
+
+    def parts(self) -> List[Part]:
+        raise NotImplementedError
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, run: int) -> None:
+        raise NotImplementedError

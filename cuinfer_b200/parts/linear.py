@@ -1,0 +1,66 @@
+"""A projection ``y = x · Wᵀ`` over one weight matrix ``[out, in]``, possibly several checkpoint matrices
+stacked along ``out`` (the reference's ``Linear``, csrc/model/layers/linear.cpp:35-95, stacks q/k/v and
+gate/up the same way and has no bias).
+
+Which kernel multiplies is decided here, per call, from the engine dtype and the shape:
+
+* float32: the FMA kernel (``gemm_generic``), true 32-bit, any shape;
+* bfloat16: the tensor-core kernels of this package where they take the shape; otherwise the library
+  product (cuBLAS through ``torch.mm``), which is what the reference uses for every projection
+  (csrc/ops/projection.cu:32-44); shapes that are not a multiple of 8 go to ``gemm_generic``.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import kernels
+from .spec import TensorSpec
+
+
+def matmul_nt(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x[M, K] @ weight[N, K]^T`` → ``[M, N]`` in ``out_dtype`` (default: x's dtype)."""
+    M, K = x.shape
+    N = weight.shape[0]
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if M == 0:
+        return out
+    if x.dtype == torch.float32:
+        kernels.gemm_generic(x, weight, out)
+        return out
+    from . import gemm_dispatch
+    gemm_dispatch.bf16_matmul_nt(x, weight, out)
+    return out
+
+
+class Linear:
+    def __init__(self, names: Sequence[str], out_features: Sequence[int], in_features: int, dtype: torch.dtype) -> None:
+        if len(names) != len(out_features):
+            raise ValueError("one out_features per name")
+        self.names = list(names)
+        self.out_features = list(out_features)
+        self.in_features = in_features
+        self.dtype = dtype
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensors(self) -> List[TensorSpec]:
+        return [TensorSpec(n, (o, self.in_features)) for n, o in zip(self.names, self.out_features)]
+
+    def load(self, store) -> None:
+        specs = self.tensors()
+        self.weight = store.get(specs[0]) if len(specs) == 1 else store.get_stacked(specs)
+        if self.weight.dtype != self.dtype:
+            self.weight = self.weight.to(self.dtype)
+
+    def tie(self, weight: torch.Tensor) -> None:
+        """Use another tensor's storage as this projection's weight (a tied output head)."""
+        if tuple(weight.shape) != (sum(self.out_features), self.in_features):
+            raise ValueError(f"tied weight has shape {list(weight.shape)}")
+        self.weight = weight
+
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        if self.weight is None:
+            raise RuntimeError(f"projection {self.names} used before its weights were loaded")
+        return matmul_nt(x, self.weight, out_dtype)
