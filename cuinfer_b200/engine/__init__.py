@@ -1,3 +1,5 @@
 from .runner import ModelRunner, StepEntry, StepError
+from .scheduler import FinishReason, Request, RequestOutput, RequestStatus, ScheduledRequest, Scheduler
 
-__all__ = ["ModelRunner", "StepEntry", "StepError"]
+__all__ = ["FinishReason", "ModelRunner", "Request", "RequestOutput", "RequestStatus", "ScheduledRequest",
+           "Scheduler", "StepEntry", "StepError"]

@@ -1,0 +1,155 @@
+"""Generation through the Python entry point and the command line, against the plain implementation."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen3
+from conftest import ROOT, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def _near_best(cfg, weights, prompt, tokens, slack):
+    """Every generated token is the plain argmax, or within ``slack`` of it (a near-tie that rounding may flip)."""
+    ids = list(prompt)
+    for t in tokens:
+        row = plain_qwen3.forward(cfg, weights, ids)[-1]
+        assert float(row.max() - row[t]) <= slack * float(row.abs().max()), (prompt, tokens, t)
+        ids.append(t)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_float32_equals_plain(model_folders, name):
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders[name]
+    folder = folders["float32"]
+    pcfg, weights = plain_qwen3.load_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, 50 + i) for i, n in enumerate([5, 17, 33, 1])]
+    llm = LLM(folder, dtype="float32", block_size=block, num_blocks=64, max_num_seqs=4, max_num_scheduled_tokens=24)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for prompt, res in zip(prompts, out):
+        assert res.finish_reason == "length" and len(res.token_ids) == 8
+        assert res.token_ids == plain_qwen3.greedy_generate(pcfg, weights, prompt, 8)
+    assert llm.engine.stats["prefill_tokens"] == sum(len(p) for p in prompts)
+    llm.engine.runner.manager.check()
+    assert not llm.engine.runner.manager.live_requests()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_bfloat16_is_near_best(model_folders, name):
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders[name]
+    folder = folders["bfloat16"]
+    pcfg, weights = plain_qwen3.load_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, 60 + i) for i, n in enumerate([9, 30, 2])]
+    llm = LLM(folder, dtype="bfloat16", block_size=block, num_blocks=64, max_num_seqs=4, max_num_scheduled_tokens=16)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    for prompt, res in zip(prompts, out):
+        _near_best(pcfg, weights, prompt, res.token_ids, 0.04)
+
+
+def test_preemption_and_recompute_give_the_same_tokens(model_folders):
+    """With so few pages that requests are preempted and recomputed, greedy float32 output is unchanged."""
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders["A"]
+    folder = folders["float32"]
+    prompts = [random_tokens(cfg["vocab_size"], n, 70 + i) for i, n in enumerate([30, 31, 20, 14])]
+    params = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    roomy = LLM(folder, dtype="float32", block_size=16, num_blocks=64, max_num_seqs=4, max_num_scheduled_tokens=64)
+    want = [r.token_ids for r in roomy.generate(prompts, params)]
+    assert roomy.engine.scheduler.num_preemptions == 0
+    tight = LLM(folder, dtype="float32", block_size=16, num_blocks=8, max_num_seqs=4, max_num_scheduled_tokens=64)
+    got = [r.token_ids for r in tight.generate(prompts, params)]
+    assert tight.engine.scheduler.num_preemptions > 0
+    assert got == want
+    tight.engine.runner.manager.check()
+
+
+def test_eos_stops_and_is_returned(model_folders):
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders["A"]
+    folder = folders["float32"]
+    pcfg, weights = plain_qwen3.load_folder(folder)
+    prompt = random_tokens(cfg["vocab_size"], 12, 80)
+    free_run = plain_qwen3.greedy_generate(pcfg, weights, prompt, 6)
+    # make the third generated token the end-of-sequence id of a copy of the model
+    import shutil, tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        shutil.copytree(folder, tmp, dirs_exist_ok=True)
+        raw = json.load(open(os.path.join(tmp, "config.json")))
+        raw["eos_token_id"] = free_run[2]
+        json.dump(raw, open(os.path.join(tmp, "config.json"), "w"))
+        llm = LLM(tmp, dtype="float32", num_blocks=16)
+        stop = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6))[0]
+        first = free_run.index(free_run[2])
+        assert stop.finish_reason == "stop" and stop.token_ids == free_run[:first + 1]
+        go_on = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))[0]
+        assert go_on.finish_reason == "length" and go_on.token_ids == free_run
+
+
+def test_entry_point_refuses_bad_requests(model_folders):
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders["A"]
+    llm = LLM(folders["float32"], dtype="float32", num_blocks=16)
+    limit = cfg["max_position_embeddings"]
+    for prompt, params, word in [
+        ([], SamplingParams(), "at least one"),
+        ([1] * limit, SamplingParams(max_tokens=1), "shorter"),
+        ([1] * 10, SamplingParams(max_tokens=limit), "exceeds"),
+        ([1, cfg["vocab_size"]], SamplingParams(max_tokens=2), "vocabulary"),
+        ([1, -1], SamplingParams(max_tokens=2), "vocabulary"),
+    ]:
+        with pytest.raises(ValueError, match=word):
+            llm.generate([prompt], params)
+    for bad in (dict(temperature=-1.0), dict(top_k=-1), dict(top_p=0.0), dict(top_p=1.5), dict(max_tokens=0)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
+    assert not llm.engine.has_requests()
+
+
+def test_sampling_is_reproducible_and_independent_of_the_batch(model_folders):
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders["B"]
+    folder = folders["float32"]
+    prompts = [random_tokens(cfg["vocab_size"], n, 90 + i) for i, n in enumerate([7, 21, 40])]
+    params = SamplingParams(temperature=0.9, top_k=50, top_p=0.9, max_tokens=10, ignore_eos=True, seed=1234)
+    a = LLM(folder, dtype="float32", block_size=block, num_blocks=32, max_num_scheduled_tokens=16, seed=1)
+    run1 = [r.token_ids for r in a.generate(prompts, params)]
+    b = LLM(folder, dtype="float32", block_size=block, num_blocks=32, max_num_scheduled_tokens=512, seed=2)
+    run2 = [r.token_ids for r in b.generate(prompts, params)]
+    assert run1 == run2                       # same seed in the request: same tokens, however prompts were cut
+    other = [r.token_ids for r in b.generate(prompts, SamplingParams(temperature=0.9, top_k=50, top_p=0.9,
+                                                                       max_tokens=10, ignore_eos=True, seed=99))]
+    assert other != run1
+
+
+def test_command_line(model_folders, tmp_path):
+    folders, cfg, block = model_folders["A"]
+    folder = folders["float32"]
+    pcfg, weights = plain_qwen3.load_folder(folder)
+    prompt = random_tokens(cfg["vocab_size"], 9, 95)
+    proc = subprocess.run(
+        [sys.executable, "-m", "cuinfer_b200", "generate", "--model", folder, "--dtype", "float32",
+         "--prompt-ids", ",".join(map(str, prompt)), "--prompt-ids", "4 5 6", "--max-tokens", "5", "--temperature", "0",
+         "--ignore-eos", "--num-blocks", "16", "--max-num-seqs", "4"],
+        capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 2 and lines[0]["prompt_token_ids"] == prompt
+    assert lines[0]["token_ids"] == plain_qwen3.greedy_generate(pcfg, weights, prompt, 5)
+    assert lines[1]["finish_reason"] == "length"
+    bad = subprocess.run([sys.executable, "-m", "cuinfer_b200", "generate", "--model", folder, "--prompt-ids", "1",
+                          "--block-size", "0"], capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert bad.returncode != 0 and "block_size" in bad.stderr
