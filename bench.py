@@ -1,0 +1,300 @@
+"""Benchmark: decode tokens/s of the Qwen3-0.6B shape at batch 8 and context 4096 on one B200, bfloat16, random
+weights; plus prefill of 2,048 tokens, decode at batch 1 and 64, and the decode step's share of the HBM roofline.
+
+``python bench.py --gpus 1 --steps K --warmup W`` prints ONE JSON line.  A step is one decode step of the whole
+batch.  ``value`` is decoded tokens per second counted on the device (CUDA events from the step's first copy to
+its sampler kernel, summed over the K steps); ``e2e`` is the same through the engine's public step call with
+host token ids in and out (each step's input copy from pinned memory and the read-back of the sampled ids are
+inside the timed region).  Between timed steps nothing is flushed: a step reads over 1 GB of weights and cache,
+far more than the 126 MB L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Qwen3-0.6B shape; benchmark context 4096, KV block size 16.
+MODEL = dict(
+    architectures=["Qwen3ForCausalLM"], num_hidden_layers=28, hidden_size=1024, num_attention_heads=16,
+    num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=151936, rope_theta=1000000.0,
+    rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096, torch_dtype="bfloat16")
+CONTEXT = 4096
+BLOCK_SIZE = 16
+PREFILL_TOKENS = 2048
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            peaks = json.load(fh)
+        peaks["source"] = "measured"
+        return peaks
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.proc = None
+        self.path = None
+
+    def start(self) -> None:
+        exe = shutil.which("nvidia-smi")
+        if not exe:
+            return
+        fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+        os.close(fd)
+        self.proc = subprocess.Popen([exe, "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as fh:
+            for line in fh:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 6:
+                    continue
+                try:
+                    clocks.append(float(parts[0]))
+                    max_clock = float(parts[1])
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[2:6]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.remove(self.path)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def weight_bytes(cfg: dict, layers: int) -> int:
+    """Bytes of every weight a decode step reads once (bfloat16): the layers' matrices and norms, the final norm
+    and the output head (the embedding table when tied; a decode step gathers only B rows of the input table)."""
+    H, I, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    Q, KV = cfg["num_attention_heads"] * d, cfg["num_key_value_heads"] * d
+    per_layer = H * (Q + 2 * KV) + Q * H + 3 * H * I + 2 * H + 2 * d
+    return 2 * (layers * per_layer + H + cfg["vocab_size"] * H)
+
+
+def kv_bytes_per_token(cfg: dict, layers: int) -> int:
+    return 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg: dict, layers: int, T: int) -> float:
+    H, I, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    Q, KV = cfg["num_attention_heads"] * d, cfg["num_key_value_heads"] * d
+    linear = 2.0 * T * layers * (H * (Q + 2 * KV) + Q * H + 3 * H * I)
+    attention = 2.0 * T * T * Q * layers          # QK^T and PV over the causal half
+    return linear + attention + 2.0 * cfg["vocab_size"] * H
+
+
+def make_engine(folder: str, batch: int, args):
+    from cuinfer_b200.config import EngineConfig
+    from cuinfer_b200.engine.core import EngineCore
+
+    pages_per_request = (CONTEXT + BLOCK_SIZE - 1) // BLOCK_SIZE
+    config = EngineConfig(model_path=folder, block_size=BLOCK_SIZE, dtype="bfloat16",
+                          num_blocks=batch * pages_per_request + 8, max_num_seqs=max(batch, 8),
+                          max_num_scheduled_tokens=8192, enable_cuda_graph=not args.disable_cuda_graph, seed=0)
+    return EngineCore(config)
+
+
+def measure_decode(folder: str, batch: int, steps: int, warmup: int, args, sample_clocks: bool = False) -> dict:
+    """Prefill ``batch`` requests so that decoding ends at CONTEXT tokens, then time ``steps`` decode steps."""
+    import torch
+
+    from cuinfer_b200 import SamplingParams, kernels
+
+    engine = make_engine(folder, batch, args)
+    total_steps = warmup + steps
+    # prompts are admitted a few per step under the token budget, so early requests decode while later ones
+    # are still being prefilled: leave room for those extra tokens below the context limit
+    prefill_steps = (batch * CONTEXT + 8191) // 8192 + 2
+    prompt_len = CONTEXT - total_steps - prefill_steps - 1
+    gen = torch.Generator().manual_seed(1234 + batch)
+    params = SamplingParams(temperature=0.0, max_tokens=CONTEXT - prompt_len, ignore_eos=True)
+    for i in range(batch):
+        prompt = torch.randint(0, MODEL["vocab_size"], (prompt_len,), generator=gen).tolist()
+        engine.add_request(f"b{i}", prompt, params)
+    # prefill (untimed): until every request has produced its first token
+    while any(r.num_output_tokens == 0 for r in engine.scheduler.requests.values()):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    ctx_start = statistics.mean(len(r.token_ids) for r in engine.scheduler.requests.values())
+    engine.runner.timing = []
+    clocks = ClockSampler()
+    if sample_clocks:
+        clocks.start()
+    launches_before = kernels.launch_count
+    graph_before = engine.runner.graph_steps
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    tokens = 0
+    for _ in range(steps):
+        tokens += sum(len(o.new_token_ids) for o in engine.step())
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    clock_info = clocks.stop() if sample_clocks else None
+    device_ms = sum(a.elapsed_time(b) for a, b in engine.runner.timing)
+    pairs = len(engine.runner.timing)
+    engine.runner.timing = None
+    assert tokens == batch * steps and pairs == steps, (tokens, pairs)
+    graph_steps = engine.runner.graph_steps - graph_before
+    per_replay = max((g.kernels_per_replay for g in engine.runner._graphs.values()), default=0)
+    launches = (kernels.launch_count - launches_before) + graph_steps * per_replay
+    ctx_mid = ctx_start + steps / 2.0        # mean tokens a request holds during the timed steps
+    out = {
+        "tokens_per_s": tokens / (device_ms / 1e3), "ms_per_step": device_ms / steps,
+        "e2e_tokens_per_s": tokens / wall, "e2e_ms_per_step": wall * 1e3 / steps, "launches": launches,
+        "graph_steps": graph_steps, "context_mid": ctx_mid, "prompt_len": prompt_len, "clocks": clock_info,
+        "h2d_bytes": (engine.runner._graphs[next(iter(engine.runner._graphs))].total * 4 if engine.runner._graphs else 0)
+        + batch * 16,
+        "d2h_bytes": batch * 4,
+    }
+    while engine.has_requests():
+        engine.abort(list(engine.scheduler.requests))
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_prefill(folder: str, args) -> dict:
+    import torch
+
+    from cuinfer_b200.engine.runner import StepEntry
+
+    engine = make_engine(folder, 1, args)
+    runner = engine.runner
+    gen = torch.Generator().manual_seed(99)
+    tokens = torch.randint(0, MODEL["vocab_size"], (PREFILL_TOKENS,), generator=gen).tolist()
+    times = []
+    for it in range(3 + 5):
+        assert runner.reserve("p", PREFILL_TOKENS)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        logits = runner.step([StepEntry("p", tokens, [PREFILL_TOKENS - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        runner.release("p")
+        if it >= 3:
+            times.append(a.elapsed_time(b))
+        assert logits.shape == (1, MODEL["vocab_size"])
+    del engine
+    torch.cuda.empty_cache()
+    return {"ms": statistics.median(times)}
+
+
+def reference_arm() -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "pip installs only the reference's Python front end into baseline/_ref; its engine (cuinfer._C) "
+                       "is a CMake build that fetches libzmq, cppzmq, msgpack-cxx and nlohmann_json from GitHub (no "
+                       "network here), it serves HTTP only, has no random-weights mode, and its kernels accept only "
+                       "hidden 1024/2048 with a downloaded checkpoint"}))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=256)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
+                        help="fewer layers than the configuration's, if memory or time needs it (reported)")
+    parser.add_argument("--disable-cuda-graph", action="store_true")
+    parser.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the prefill measurement")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    if args.steps + args.warmup + 40 >= CONTEXT:
+        parser.error("steps + warmup must stay below the context length")
+
+    import torch
+
+    from cuinfer_b200.weights import write_random_model
+
+    peaks = load_peaks()
+    cfg = dict(MODEL, num_hidden_layers=args.layers)
+    tmp = tempfile.mkdtemp(prefix="cuinfer_b200_bench_")
+    try:
+        write_random_model(tmp, cfg, seed=0, std=0.02, dtype="bfloat16")
+        main_run = measure_decode(tmp, args.batch, args.steps, args.warmup, args, sample_clocks=True)
+        points, prefill = {}, None
+        if not args.skip_points:
+            for b in (1, 64):
+                r = measure_decode(tmp, b, min(args.steps, 128), args.warmup, args)
+                points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+            p = measure_prefill(tmp, args)
+            flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+            prefill = {"value": round(PREFILL_TOKENS / (p["ms"] / 1e3), 1), "tokens": PREFILL_TOKENS,
+                       "ms": round(p["ms"], 3), "frac": round(flops / (p["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+    step_bytes = weight_bytes(cfg, args.layers) + args.batch * main_run["context_mid"] * kv_bytes_per_token(cfg, args.layers)
+    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2048 tokens; % of roofline",
+        "value": round(main_run["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) seed 0, uniform-random token ids", "impl": "ours",
+        "config": {
+            "model": "Qwen3-0.6B shape (BASELINE configs[2])", "layers": args.layers,
+            "layers_full": MODEL["num_hidden_layers"], "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+            "vocab": cfg["vocab_size"], "tied_embeddings": True, "global_batch": args.batch, "seq_len": CONTEXT,
+            "prompt_len": main_run["prompt_len"], "kv_block_size": BLOCK_SIZE, "parallelism": "single GPU",
+            "cuda_graph": not args.disable_cuda_graph, "l2": "no flush: each step reads >1 GB, far more than the 126 MB L2",
+            "peaks": peaks["source"],
+        },
+        "e2e": {"value": round(main_run["e2e_tokens_per_s"], 1), "unit": "tokens/s",
+                "ms_per_step": round(main_run["e2e_ms_per_step"], 4),
+                "h2d_bytes_per_step": main_run["h2d_bytes"], "d2h_bytes_per_step": main_run["d2h_bytes"]},
+        "gpu_launches": main_run["launches"],
+        "clocks": main_run["clocks"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+    if points:
+        line["points"] = points
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -67,11 +67,16 @@ class EngineCore:
         for s in scheduled:
             self.stats["prefill_tokens" if s.is_prefill else "decode_tokens"] += len(s.tokens)
         wanted = [s for s in scheduled if s.needs_sampling]
-        logits = self.runner.step(entries)
+        if len(wanted) == len(entries) and self.runner.can_use_graph(entries):
+            logits = self.runner.decode_step(entries)
+        else:
+            logits = self.runner.step(entries)
         if not wanted:
+            self.runner.mark_device_end()
             return []
         ids = self.sampler.sample(
             logits, [s.request.params for s in wanted], [s.request.key for s in wanted],
             [s.request.num_output_tokens for s in wanted])
+        self.runner.mark_device_end()
         host = ids.cpu().tolist()
         return [(s.request.request_id, tok) for s, tok in zip(wanted, host)]

@@ -104,8 +104,13 @@ class ModelRunner:
                 self._run_cache[run] = (src, src == run)
         self._ring = _PinnedRing()
         self._arena: Optional[torch.Tensor] = None
+        self._graphs: Dict[int, "DecodeGraph"] = {}
         self.steps_run = 0
         self.tokens_run = 0
+        self.graph_steps = 0
+        # when a list: (start, end) CUDA events of every step's device work are appended (the benchmark reads them)
+        self.timing: Optional[list] = None
+        self._timing_start: Optional[torch.cuda.Event] = None
 
     # ---- sizing ------------------------------------------------------------------------------------
     def page_bytes(self) -> int:
@@ -254,6 +259,7 @@ class ModelRunner:
         if self._arena is None or self._arena.numel() < total:
             self._arena = torch.empty(max(4096, 1 << (total - 1).bit_length()), dtype=torch.int32, device=self.device)
         dev = self._arena[:total]
+        self.mark_device_begin()
         dev.copy_(pinned[:total], non_blocking=True)
         self._ring.mark(ring_idx)
 
@@ -289,3 +295,188 @@ class ModelRunner:
         self.steps_run += 1
         self.tokens_run += ctx.num_tokens
         return logits
+
+    def mark_device_begin(self) -> None:
+        if self.timing is not None:
+            self._timing_start = torch.cuda.Event(enable_timing=True)
+            self._timing_start.record()
+
+    def mark_device_end(self) -> None:
+        if self.timing is not None and self._timing_start is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            self.timing.append((self._timing_start, end))
+            self._timing_start = None
+
+    # ---- decode steps as CUDA graphs ---------------------------------------------------------------------
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+    def can_use_graph(self, entries: Sequence[StepEntry]) -> bool:
+        return (self.config.enable_cuda_graph and len(entries) <= self.GRAPH_BUCKETS[-1]
+                and all(len(e.tokens) == 1 for e in entries))
+
+    def decode_graph(self, rows: int) -> "DecodeGraph":
+        bucket = next(b for b in self.GRAPH_BUCKETS if b >= rows)
+        graph = self._graphs.get(bucket)
+        if graph is None:
+            stride = (self.max_model_len + self.page_size - 1) // self.page_size
+            graph = DecodeGraph(self, bucket, stride)
+            graph.capture()
+            self._graphs[bucket] = graph
+        return graph
+
+    def decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """One decode step (every entry brings one token and wants its logits) by graph replay.
+        Returns float32 logits ``[len(entries), vocab]``; the tensor is overwritten by the next decode step."""
+        self._validate(entries)
+        self.storage.zero_slots(self.manager.take_newly_admitted())
+        graph = self.decode_graph(len(entries))
+        graph.upload(entries)
+        logits = graph.replay()
+        for e in entries:
+            self.manager.commit(e.request_id, 1)
+        self.steps_run += 1
+        self.graph_steps += 1
+        self.tokens_run += len(entries)
+        return logits[:len(entries)]
+
+
+class DecodeGraph:
+    """A CUDA graph of one decode step for a fixed number of request rows (a bucket).
+
+    The reference captures its forward pass per token-count bucket (powers of two) and launches attention
+    between graph segments (csrc/executor/cuda_graph_runner.cpp:11-22, :51-115).  Here a bucket's whole
+    step — embedding, every layer with its attention, final norm and output head — is one graph: the
+    attention kernels read lengths and block tables from device memory, so their launch shape does not
+    depend on the batch.  Rows beyond the live requests are padding: token 0, position 0, no cache write
+    (slot -1), an empty block table; their logits are never read.
+
+    All per-step inputs live in one device arena that is refreshed by a single copy from pinned memory.
+    """
+
+    def __init__(self, runner: "ModelRunner", rows: int, table_stride: int) -> None:
+        self.runner = runner
+        self.rows = rows
+        self.stride = table_stride
+        G = len(runner.groups)
+        B, P = rows, table_stride
+        self.layout = {}
+        off = 0
+        for name, n in [("tok", B), ("pos", B), ("treq", B), ("qsl", B + 1), ("sl", B), ("slots", B), ("want", B)]:
+            self.layout[name] = (off, n)
+            off += n
+        for g in range(G):
+            self.layout[f"sm{g}"] = (off, B)
+            off += B
+            self.layout[f"bt{g}"] = (off, B * P)
+            off += B * P
+        self.total = off
+        self.pinned = [torch.empty(off, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.events: List[Optional[torch.cuda.Event]] = [None, None]
+        self.turn = 0
+        self.arena = torch.zeros(off, dtype=torch.int32, device=runner.device)
+        for buf in self.pinned:
+            host = buf.numpy()
+            host[:] = 0
+            self._fill_constants(host)
+        self.ctx = self._context()
+        self.logits: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.kernels_per_replay = 0
+
+    def _view(self, host: np.ndarray, name: str) -> np.ndarray:
+        off, n = self.layout[name]
+        return host[off:off + n]
+
+    def _dev(self, name: str) -> torch.Tensor:
+        off, n = self.layout[name]
+        return self.arena[off:off + n]
+
+    def _fill_constants(self, host: np.ndarray) -> None:
+        B = self.rows
+        self._view(host, "treq")[:] = np.arange(B, dtype=np.int32)
+        self._view(host, "qsl")[:] = np.arange(B + 1, dtype=np.int32)
+        self._view(host, "want")[:] = np.arange(B, dtype=np.int32)
+        self._view(host, "sl")[:] = 1
+        for g in range(len(self.runner.groups)):       # padding rows never write to the cache
+            self._view(host, f"sm{g}")[:] = -1
+            self._view(host, f"bt{g}")[:] = -1
+
+    def _context(self) -> StepContext:
+        r = self.runner
+        B, P = self.rows, self.stride
+        groups = {g: GroupView(r.page_size, self._dev(f"bt{g}").view(B, P), self._dev(f"sm{g}"))
+                  for g in range(len(r.groups))}
+        ctx = StepContext(
+            num_tokens=B, num_requests=B, token_ids=self._dev("tok"), positions=self._dev("pos"),
+            token_request=self._dev("treq"), query_start_loc=self._dev("qsl"), seq_lens=self._dev("sl"),
+            state_slots=self._dev("slots"), query_start_loc_host=list(range(B + 1)), seq_lens_host=[],
+            state_slots_host=[], max_query_len=1, max_seq_len=r.max_model_len, groups=groups, decode_only=True)
+        for run, (src, writes) in r._run_cache.items():
+            ctx.kv[run] = PagedKV(r.storage.run_cache[src], groups[r.storage.run_group[src]], writes)
+        ctx.state = r.storage.state
+        return ctx
+
+    def _forward(self) -> torch.Tensor:
+        stream = self.runner.model.forward(self.ctx)
+        return self.runner.model.logits(stream, self._dev("want"))
+
+    def upload(self, entries: Sequence[StepEntry]) -> None:
+        r = self.runner
+        mgr = r.manager
+        i = self.turn
+        self.turn ^= 1
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        host = self.pinned[i].numpy()
+        B, P, ps = self.rows, self.stride, r.page_size
+        n = len(entries)
+        tok, pos, sl, slots = (self._view(host, k) for k in ("tok", "pos", "sl", "slots"))
+        starts = [mgr.num_tokens(e.request_id) for e in entries]
+        tok[:n] = [e.tokens[0] for e in entries]
+        tok[n:] = 0
+        pos[:n] = starts
+        pos[n:] = 0
+        sl[:n] = np.asarray(starts, dtype=np.int32) + 1
+        sl[n:] = 1
+        slots[:n] = [mgr.slot(e.request_id) for e in entries]
+        slots[n:] = 0
+        for g in range(len(r.groups)):
+            sm = self._view(host, f"sm{g}")
+            bt = self._view(host, f"bt{g}").reshape(B, P)
+            bt[n:, :] = -1
+            sm[n:] = -1
+            for row, (e, start) in enumerate(zip(entries, starts)):
+                table = mgr.block_table(e.request_id, g)
+                k = len(table)
+                if k > P:
+                    raise StepError(f"request {e.request_id!r} holds {k} pages, more than the graph's table stride {P}")
+                bt[row, :k] = table
+                bt[row, k:] = -1
+                page = table[start // ps]
+                if page < 0:
+                    raise StepError(f"request {e.request_id!r}: its new token has no page in group {g}")
+                sm[row] = page * ps + start % ps
+        r.mark_device_begin()
+        self.arena.copy_(self.pinned[i], non_blocking=True)
+        if self.events[i] is None:
+            self.events[i] = torch.cuda.Event()
+        self.events[i].record()
+
+    def capture(self) -> None:
+        from .. import kernels
+
+        # one eager run first: library handles and workspaces are created outside the capture
+        self.arena.copy_(self.pinned[0], non_blocking=True)
+        before = kernels.launch_count
+        self._forward()
+        self.kernels_per_replay = kernels.launch_count - before
+        torch.cuda.synchronize(self.runner.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = self._forward()
+        torch.cuda.synchronize(self.runner.device)
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.logits
