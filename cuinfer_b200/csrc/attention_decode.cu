@@ -1,0 +1,351 @@
+// Paged attention for decode steps (one query token per request), bfloat16, split over the keys.
+//
+// The reference runs decode tokens through its one attention kernel with 64-row tiles, of which a decoded
+// token fills nq/nkv rows, and one CTA walks all keys of a request (csrc/ops/paged_attention.cu:133-383).
+// Decode is a stream of the cache through the SMs, so here the keys of a (request, kv head) are split over
+// `splits` CTAs, and inside a CTA over 4 warps; each warp copies its 16-key blocks into a private
+// shared-memory ring with cp.async (no block-wide barrier in the loop), multiplies the group's query heads
+// (rows of one m16 tile) with them on the tensor cores, and keeps a running softmax in base 2.  Warps are
+// merged in shared memory, CTAs through a scratch buffer: every CTA writes its partial (max, sum, weighted
+// values) and bumps a counter; the last CTA of a (request, kv head) combines all partials and writes the
+// output, then resets the counter so that the kernel can be replayed from a CUDA graph.
+//
+// Scratch layout (float32): part_o[(request * nkv + kvh) * splits + split][g][D], part_ml[...][g][2].
+// Cache layout of one layer: [page][0 = keys, 1 = values][kv head][slot in page][D].
+#include "mma_utils.cuh"
+
+namespace cib {
+
+constexpr int kDecWarps = 4;
+constexpr int kDecStages = 3;
+constexpr int kDecKeys = 16;   // keys per warp block
+
+template <int D>
+struct DecodeSmem {
+    // per warp: kDecStages x (K block + V block), each [16][D] bf16, XOR-swizzled in 16-byte chunks
+    static constexpr int kBlockBytes = kDecKeys * D * 2;
+    static constexpr int kWarpBytes = kDecStages * 2 * kBlockBytes;
+    static constexpr int kTotal = kDecWarps * kWarpBytes;
+};
+
+template <int D>
+__device__ __forceinline__ void load_block(__nv_bfloat16* sK, __nv_bfloat16* sV, const __nv_bfloat16* cache,
+                                           const int* table, int key0, int key_end, int page_size, int num_pages,
+                                           int nkv, int kvh, int lane) {
+    constexpr int kChunks = D / 8;             // 16-byte chunks per row
+    const int row = lane >> 1;
+    const int half = lane & 1;
+    const int j = key0 + row;
+    bool valid = j < key_end;
+    int page = 0, off = 0;
+    if (valid) {
+        page = table[j / page_size];
+        off = j % page_size;
+        valid = page >= 0 && page < num_pages;
+    }
+    const size_t head_stride = (size_t)page_size * D;
+    const __nv_bfloat16* kp = cache + (((size_t)(valid ? page : 0) * 2 + 0) * nkv + kvh) * head_stride + (size_t)off * D;
+    const __nv_bfloat16* vp = kp + (size_t)nkv * head_stride;
+#pragma unroll
+    for (int c = 0; c < kChunks / 2; ++c) {
+        const int chunk = half * (kChunks / 2) + c;
+        const int sw = (chunk ^ (row & 7)) * 8;
+        cp_async16(sK + row * D + sw, kp + chunk * 8, valid);
+        cp_async16(sV + row * D + sw, vp + chunk * 8, valid);
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kDecWarps * 32)
+paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
+                              int out_stride, const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
+                              const int* __restrict__ block_table, int table_stride,
+                              const int* __restrict__ seq_lens, int nq, int nkv, float scale_log2, int window,
+                              int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                              int* __restrict__ counters) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+    const int g = nq / nkv;
+    const int quad = lane & 3, qrow = lane >> 2;
+
+    const int seq_len = seq_lens[r];
+    const int pos = seq_len - 1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int span = max(0, seq_len - lo);
+    int chunk = (span + splits - 1) / splits;
+    chunk = (chunk + kDecKeys - 1) / kDecKeys * kDecKeys;
+    const int k_begin = lo + split * chunk;
+    const int k_end = min(seq_len, k_begin + chunk);
+    const int* table = block_table + (size_t)r * table_stride;
+
+    // ---- query fragments: rows 0..g-1 are the heads of this kv head, the rest are zero ----
+    uint32_t qf[D / 16][4];
+    {
+        const __nv_bfloat16* qp = q + (size_t)r * q_stride + (size_t)kvh * g * D;
+#pragma unroll
+        for (int kt = 0; kt < D / 16; ++kt) {
+            const int c0 = kt * 16 + quad * 2;
+            qf[kt][0] = qrow < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)qrow * D + c0) : 0u;
+            qf[kt][1] = qrow + 8 < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)(qrow + 8) * D + c0) : 0u;
+            qf[kt][2] = qrow < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)qrow * D + c0 + 8) : 0u;
+            qf[kt][3] = qrow + 8 < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)(qrow + 8) * D + c0 + 8) : 0u;
+        }
+    }
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw + (size_t)warp * DecodeSmem<D>::kWarpBytes);
+    auto stage_k = [&](int s) { return ring + (size_t)s * 2 * kDecKeys * D; };
+    auto stage_v = [&](int s) { return ring + (size_t)s * 2 * kDecKeys * D + kDecKeys * D; };
+
+    const int total_blocks = k_end > k_begin ? (k_end - k_begin + kDecKeys - 1) / kDecKeys : 0;
+    const int my_blocks = total_blocks > warp ? (total_blocks - warp + kDecWarps - 1) / kDecWarps : 0;
+    auto block_key = [&](int i) { return k_begin + (i * kDecWarps + warp) * kDecKeys; };
+
+#pragma unroll
+    for (int s = 0; s < kDecStages - 1; ++s) {
+        if (s < my_blocks) load_block<D>(stage_k(s), stage_v(s), cache, table, block_key(s), k_end, page_size, num_pages, nkv, kvh, lane);
+        cp_async_commit();
+    }
+    for (int i = 0; i < my_blocks; ++i) {
+        cp_async_wait<kDecStages - 2>();
+        __syncwarp();
+        {
+            const int nxt = i + kDecStages - 1;
+            if (nxt < my_blocks)
+                load_block<D>(stage_k(nxt % kDecStages), stage_v(nxt % kDecStages), cache, table, block_key(nxt), k_end,
+                              page_size, num_pages, nkv, kvh, lane);
+            cp_async_commit();
+        }
+        const __nv_bfloat16* sK = stage_k(i % kDecStages);
+        const __nv_bfloat16* sV = stage_v(i % kDecStages);
+        const int key0 = block_key(i);
+
+        // ---- S = Q K^T for 16 keys ----
+        float s[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        {
+            const int mat = lane >> 3, rr = lane & 7;
+            const int krow = (mat >> 1) * 8 + rr;
+#pragma unroll
+            for (int kt = 0; kt < D / 16; ++kt) {
+                const int chunkc = 2 * kt + (mat & 1);
+                uint32_t b[4];
+                ldmatrix_x4(b, smem_u32(sK + krow * D + ((chunkc ^ (krow & 7)) * 8)));
+                mma_bf16_16816(s[0], qf[kt], b[0], b[1]);
+                mma_bf16_16816(s[1], qf[kt], b[2], b[3]);
+            }
+        }
+        // ---- mask, running softmax (base 2) ----
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + n * 8 + quad * 2 + (e & 1);
+                const float v = key < k_end ? s[n][e] * scale_log2 : -INFINITY;
+                s[n][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m_run[h], mx[h]);
+            corr[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_new);
+            m_run[h] = m_new;
+            l_run[h] *= corr[h];
+        }
+        uint32_t pf[4];
+        {
+            float p[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float mref = m_run[e >> 1];
+                    p[n][e] = (s[n][e] == -INFINITY || mref == -INFINITY) ? 0.f : exp2f(s[n][e] - mref);
+                    l_run[e >> 1] += p[n][e];
+                }
+            pf[0] = pack_bf16(p[0][0], p[0][1]);
+            pf[1] = pack_bf16(p[0][2], p[0][3]);
+            pf[2] = pack_bf16(p[1][0], p[1][1]);
+            pf[3] = pack_bf16(p[1][2], p[1][3]);
+        }
+        // ---- O = O * corr + P V ----
+        {
+            const int mat = lane >> 3, rr = lane & 7;
+            const int vrow = (mat & 1) * 8 + rr;
+#pragma unroll
+            for (int nt = 0; nt < D / 16; ++nt) {
+                const int chunkc = 2 * nt + (mat >> 1);
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, smem_u32(sV + vrow * D + ((chunkc ^ (vrow & 7)) * 8)));
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    float* acc = o[2 * nt + t];
+                    acc[0] *= corr[0]; acc[1] *= corr[0]; acc[2] *= corr[1]; acc[3] *= corr[1];
+                }
+                mma_bf16_16816(o[2 * nt], pf, b[0], b[1]);
+                mma_bf16_16816(o[2 * nt + 1], pf, b[2], b[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();     // all rings are free: reuse shared memory for the merge of the warps
+
+    // ---- merge the warps (only the g real rows) ----
+    float* sm_m = reinterpret_cast<float*>(smem_raw);             // [warps][16]
+    float* sm_l = sm_m + kDecWarps * 16;                          // [warps][16]
+    float* sm_o = sm_l + kDecWarps * 16;                          // [warps][g][D]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = l_run[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = qrow + 8 * h;
+        if (quad == 0) { sm_m[warp * 16 + row] = m_run[h]; sm_l[warp * 16 + row] = l; }
+        if (row < g) {
+#pragma unroll
+            for (int nt = 0; nt < D / 8; ++nt) {
+                float* dst = sm_o + ((size_t)(warp * g + row)) * D + nt * 8 + quad * 2;
+                dst[0] = o[nt][2 * h];
+                dst[1] = o[nt][2 * h + 1];
+            }
+        }
+    }
+    __syncthreads();
+    const size_t part_base = ((size_t)r * nkv + kvh) * splits + split;
+    for (int idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
+        const int row = idx / D, dim = idx - row * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
+        float L = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < kDecWarps; ++w) {
+                const float mw = sm_m[w * 16 + row];
+                const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+                L += sm_l[w * 16 + row] * f;
+                O += sm_o[((size_t)(w * g + row)) * D + dim] * f;
+            }
+        }
+        if (splits == 1) {
+            out[(size_t)r * out_stride + (size_t)(kvh * g + row) * D + dim] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            part_o[(part_base * g + row) * D + dim] = O;
+            if (dim == 0) {
+                part_ml[(part_base * g + row) * 2 + 0] = M;
+                part_ml[(part_base * g + row) * 2 + 1] = L;
+            }
+        }
+    }
+    if (splits == 1) return;
+
+    // ---- the last CTA of this (request, kv head) combines the splits ----
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int done = atomicAdd(&counters[r * nkv + kvh], 1);
+        s_last = done == splits - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const size_t base = ((size_t)r * nkv + kvh) * splits;
+    for (int idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
+        const int row = idx / D, dim = idx - row * D;
+        float M = -INFINITY;
+        for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, __ldcg(&part_ml[((base + sp) * g + row) * 2]));
+        float L = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+            for (int sp = 0; sp < splits; ++sp) {
+                const float ms = __ldcg(&part_ml[((base + sp) * g + row) * 2]);
+                const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+                L += __ldcg(&part_ml[((base + sp) * g + row) * 2 + 1]) * f;
+                O += __ldcg(&part_o[((base + sp) * g + row) * D + dim]) * f;
+            }
+        }
+        out[(size_t)r * out_stride + (size_t)(kvh * g + row) * D + dim] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+    if (threadIdx.x == 0) counters[r * nkv + kvh] = 0;
+}
+
+template <int D>
+static int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* cache, int num_pages,
+                         int page_size, const int* block_table, int table_stride, const int* seq_lens,
+                         int num_requests, int nq, int nkv, float scale, int window, int splits, float* part_o,
+                         float* part_ml, int* counters, cudaStream_t stream) {
+    const int g = nq / nkv;
+    size_t smem = DecodeSmem<D>::kTotal;
+    const size_t merge = (size_t)(2 * kDecWarps * 16 + kDecWarps * g * D) * sizeof(float);
+    if (merge > smem) smem = merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) {
+            set_error("paged_attention_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
+            return -2;
+        }
+        configured = true;
+    }
+    CIB_REQUIRE(smem <= 200 * 1024, "paged_attention_decode: needs %zu bytes of shared memory", smem);
+    dim3 grid(splits, nkv, num_requests);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    paged_attention_decode_kernel<D><<<grid, kDecWarps * 32, smem, stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache, num_pages,
+        page_size, block_table, table_stride, seq_lens, nq, nkv, scale_log2, window, splits, part_o, part_ml, counters);
+    CIB_LAUNCH_CHECK("paged_attention_decode");
+    return 0;
+}
+
+}  // namespace cib
+
+using namespace cib;
+
+// Head sizes this kernel takes; others are refused (the caller falls back to the all-sizes kernel).
+extern "C" int cib_paged_attention_decode_supports(int head_dim, int nq, int nkv) {
+    return (head_dim == 64 || head_dim == 128 || head_dim == 256) && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16;
+}
+
+// Floats of scratch that `splits` splits need: part_o then part_ml, laid out one after the other.
+extern "C" long long cib_paged_attention_decode_scratch_floats(int num_requests, int nq, int head_dim, int splits) {
+    return (long long)num_requests * nq * splits * (head_dim + 2);
+}
+
+// One query token per request.  `scratch` holds cib_paged_attention_decode_scratch_floats floats (unused when
+// splits == 1); `counters` holds num_requests * nkv ints that are zero before the first call (the kernel leaves
+// them zero).
+extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* cache,
+                                          int num_pages, int page_size, const int* block_table, int table_stride,
+                                          const int* seq_lens, int num_requests, int nq, int nkv, int head_dim,
+                                          float scale, int window, int splits, float* scratch, int* counters,
+                                          cudaStream_t stream) {
+    CIB_REQUIRE(cib_paged_attention_decode_supports(head_dim, nq, nkv),
+                "paged_attention_decode: head_dim %d with %d/%d heads is not taken by this kernel (64, 128 or 256; at most 16 query heads per kv head)",
+                head_dim, nq, nkv);
+    CIB_REQUIRE(num_requests >= 0 && splits >= 1 && splits <= 64, "paged_attention_decode: bad sizes R=%d splits=%d", num_requests, splits);
+    CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0, "paged_attention_decode: bad cache geometry");
+    CIB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4) == 0, "paged_attention_decode: q rows must be 4-byte aligned");
+    CIB_REQUIRE(splits == 1 || (scratch && counters), "paged_attention_decode: splits need scratch and counters");
+    CIB_REQUIRE(num_requests <= 65535 && nkv <= 65535, "paged_attention_decode: grid too large");
+    if (num_requests == 0) return 0;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)num_requests * nq * splits * head_dim : nullptr;
+    switch (head_dim) {
+        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream);
+        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream);
+        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream);
+    }
+    return -1;
+}

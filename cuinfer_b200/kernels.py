@@ -69,6 +69,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_silu_mul": [_P, _P, _I, _I, _I, _P],
         "cib_qk_norm_rope_kv_write": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+        "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
         "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
     }
@@ -76,6 +77,10 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = _I
+    lib.cib_paged_attention_decode_supports.argtypes = [_I, _I, _I]
+    lib.cib_paged_attention_decode_supports.restype = _I
+    lib.cib_paged_attention_decode_scratch_floats.argtypes = [_I, _I, _I, _I]
+    lib.cib_paged_attention_decode_scratch_floats.restype = ctypes.c_longlong
 
 
 def _check(rc: int, name: str) -> None:
@@ -224,6 +229,57 @@ def paged_attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Ten
         _cuda(token_request, "token_request", torch.int32), T, num_q_heads, num_kv_heads, head_dim, float(scale),
         int(window), _stream())
     _check(rc, "paged_attention_generic")
+    _count()
+
+
+_decode_counters: dict = {}
+_retired: list = []
+
+
+def paged_attention_decode_supports(head_dim: int, num_q_heads: int, num_kv_heads: int) -> bool:
+    return bool(library().cib_paged_attention_decode_supports(head_dim, num_q_heads, num_kv_heads))
+
+
+def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int:
+    """How many CTAs share the keys of one (request, kv head): enough CTAs to fill the 148 SMs about four
+    times over, but at least 64 keys each."""
+    want = -(-592 // max(1, num_requests * num_kv_heads))
+    by_len = max(1, max_seq_len // 64)
+    return max(1, min(32, want, by_len))
+
+
+def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                           seq_lens: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                           window: int, splits: int) -> None:
+    """bfloat16 attention of one query token per request (``q[r, :nq*d]``) over the paged cache, the keys of
+    every (request, kv head) split over ``splits`` CTAs.  Allocates the partial-result scratch with torch."""
+    R = q.shape[0]
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("paged_attention_decode: bfloat16 only")
+    if q.stride(1) != 1 or out.stride(1) != 1 or out.shape != (R, num_q_heads * head_dim):
+        raise KernelError("paged_attention_decode: q/out rows must be dense and out [R, nq*d]")
+    scratch = None
+    counters = None
+    if splits > 1:
+        n = library().cib_paged_attention_decode_scratch_floats(R, num_q_heads, head_dim, splits)
+        scratch = torch.empty(n, dtype=torch.float32, device=q.device)
+        need = R * num_kv_heads
+        counters = _decode_counters.get(q.device.index)
+        if counters is None or counters.numel() < need:
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError("paged_attention_decode: the split counters must exist before a graph capture "
+                                  "(run the step once eagerly first)")
+            if counters is not None:
+                _retired.append(counters)      # a captured graph may still point at the old buffer
+            counters = torch.zeros(max(need, 4096), dtype=torch.int32, device=q.device)
+            _decode_counters[q.device.index] = counters
+    rc = library().cib_paged_attention_decode(
+        _cuda(q, "q", contiguous=False), q.stride(0), _cuda(out, "out", contiguous=False), out.stride(0),
+        _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
+        block_table.stride(0), _cuda(seq_lens, "seq_lens", torch.int32), R, num_q_heads, num_kv_heads, head_dim,
+        float(scale), int(window), int(splits), scratch.data_ptr() if scratch is not None else None,
+        counters.data_ptr() if counters is not None else None, _stream())
+    _check(rc, "paged_attention_decode")
     _count()
 
 

@@ -13,6 +13,12 @@ from .context import PagedKV, StepContext
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepContext, num_heads: int,
                     num_kv_heads: int, head_dim: int, scale: float, window: int) -> None:
+    if (qkv.dtype == torch.bfloat16 and ctx.decode_only
+            and kernels.paged_attention_decode_supports(head_dim, num_heads, num_kv_heads)):
+        splits = kernels.decode_splits(ctx.num_requests, num_kv_heads, max(1, ctx.max_seq_len))
+        kernels.paged_attention_decode(qkv, out, kv.cache, kv.group.block_table, ctx.seq_lens, num_heads,
+                                       num_kv_heads, head_dim, scale, window, splits)
+        return
     kernels.paged_attention_generic(
         qkv, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens, ctx.token_request,
         num_heads, num_kv_heads, head_dim, scale, window)

@@ -1,0 +1,313 @@
+"""Each CUDA kernel alone against a plain 32-bit reference of the same op, at sizes other than the engine's."""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _k():
+    from cuinfer_b200 import kernels
+    return kernels
+
+
+def rand(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def close(got, want, tol):
+    got, want = got.float().cpu(), want.float().cpu()
+    err = float((got - want).abs().max()) / max(1e-12, float(want.abs().max()))
+    assert err <= tol, f"error {err:.3e} of the largest value, allowed {tol:.1e}"
+
+
+TOL = {torch.float32: 2e-6, torch.bfloat16: 1.2e-2}
+
+
+# ---- embedding, norm, gather, silu ------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V, H", [(517, 80), (1000, 1027), (64, 4096)])
+def test_embedding_gather(dtype, V, H):
+    k = _k()
+    table = rand(V, H, seed=1, dtype=dtype).to(DEV)
+    ids = torch.tensor([0, V - 1, 3, 3, V // 2], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, H, dtype=torch.float32, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k.embedding_gather(ids, table, out, flag)
+    assert torch.equal(out.cpu(), table.float().cpu()[ids.cpu().long()]) and int(flag.item()) == 0
+    bad = torch.tensor([1, V], dtype=torch.int32, device=DEV)
+    out2 = torch.ones(2, H, dtype=torch.float32, device=DEV)
+    k.embedding_gather(bad, table, out2, flag)
+    assert int(flag.item()) == 1 and float(out2[1].abs().max()) == 0.0        # out of range: zeros and a flag, no fault
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H", [80, 1027, 5120])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(dtype, H, wdtype):
+    k = _k()
+    if dtype == torch.float32 and wdtype == torch.bfloat16:
+        pytest.skip("a 32-bit engine holds 32-bit gains")
+    rows = 7
+    res = rand(rows, H, seed=2, scale=3.0)
+    delta = rand(rows, H, seed=3, dtype=dtype)
+    w = (1 + rand(H, seed=4, scale=0.2)).to(wdtype)
+    eps = 3e-5
+    r_dev = res.clone().to(DEV)
+    out = torch.empty(rows, H, dtype=dtype, device=DEV)
+    k.add_rmsnorm(r_dev, delta.to(DEV), w.to(DEV), eps, out)
+    x = res + delta.float()
+    close(r_dev, x, 1e-7)
+    close(out, P.rms_norm(x, w.float(), eps), TOL[dtype])
+    # without a delta the residual is untouched
+    r2 = res.clone().to(DEV)
+    k.add_rmsnorm(r2, None, w.to(DEV), eps, out)
+    assert torch.equal(r2.cpu(), res)
+    close(out, P.rms_norm(res, w.float(), eps), TOL[dtype])
+
+
+def test_gather_rows():
+    k = _k()
+    res, delta = rand(9, 83, seed=5), rand(9, 83, seed=6, dtype=torch.bfloat16)
+    idx = torch.tensor([8, 0, 4, 4], dtype=torch.int32)
+    out = torch.empty(4, 83, dtype=torch.float32, device=DEV)
+    k.gather_rows(res.to(DEV), delta.to(DEV), idx.to(DEV), out)
+    close(out, (res + delta.float())[idx.long()], 1e-7)
+    k.gather_rows(res.to(DEV), None, idx.to(DEV), out)
+    assert torch.equal(out.cpu(), res[idx.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("I", [176, 333, 3072])
+def test_silu_mul(dtype, I):
+    k = _k()
+    gu = rand(5, 2 * I, seed=7, scale=3.0, dtype=dtype)
+    out = torch.empty(5, I, dtype=dtype, device=DEV)
+    k.silu_mul(gu.to(DEV), out)
+    g, u = gu.float()[:, :I], gu.float()[:, I:]
+    close(out, g / (1 + torch.exp(-g)) * u, TOL[dtype])
+
+
+# ---- matrix product ---------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M, N, K", [(1, 1000, 96), (7, 517, 80), (65, 130, 33), (200, 64, 1027)])
+@pytest.mark.parametrize("dtypes", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                    (torch.bfloat16, torch.float32)])
+def test_gemm_generic(M, N, K, dtypes):
+    k = _k()
+    din, dout = dtypes
+    a, w = rand(M, K, seed=8, dtype=din), rand(N, K, seed=9, dtype=din)
+    out = torch.empty(M, N, dtype=dout, device=DEV)
+    k.gemm_generic(a.to(DEV), w.to(DEV), out)
+    want = a.double() @ w.double().T
+    close(out, want, 1e-5 if dout == torch.float32 else 6e-3)
+    # a row's result does not depend on the rows beside it
+    one = torch.empty(1, N, dtype=dout, device=DEV)
+    k.gemm_generic(a[M // 2:M // 2 + 1].to(DEV), w.to(DEV), one)
+    assert torch.equal(one[0].cpu(), out[M // 2].cpu())
+
+
+# ---- q/k norm + rotary + cache write ------------------------------------------------------------------------
+
+def paged_cache(k_dense, v_dense, page_size, num_pages, seed, dtype):
+    """Scatter per-request dense [n, nkv, d] keys/values into shuffled pages.
+    Returns (cache [pages, 2, nkv, ps, d], tables list, slot list per request)."""
+    g = torch.Generator().manual_seed(seed)
+    nkv, d = k_dense[0].shape[1:]
+    cache = (torch.randn(num_pages, 2, nkv, page_size, d, generator=g) * 50).to(dtype)   # stale garbage everywhere
+    order = torch.randperm(num_pages, generator=g).tolist()
+    tables = []
+    for kd, vd in zip(k_dense, v_dense):
+        n = kd.shape[0]
+        pages = [order.pop() for _ in range((n + page_size - 1) // page_size)]
+        tables.append(pages)
+        for j in range(n):
+            cache[pages[j // page_size], 0, :, j % page_size] = kd[j].to(dtype)
+            cache[pages[j // page_size], 1, :, j % page_size] = vd[j].to(dtype)
+    return cache, tables
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq, nkv, d, rot", [(6, 3, 48, 48), (4, 1, 80, 32), (16, 8, 128, 128), (2, 2, 16, 0)])
+def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, rot):
+    k = _k()
+    T, ps, pages = 11, 4, 9
+    width = (nq + 2 * nkv) * d
+    qkv = rand(T, width, seed=10, dtype=dtype)
+    positions = torch.tensor([0, 1, 2, 3, 4, 5, 17, 18, 40, 41, 42], dtype=torch.int32)
+    slots = torch.tensor([4, 5, 6, 7, 8, 9, 30, 31, 0, 1, -1], dtype=torch.int32)     # the last token is padding
+    qw, kw = 1 + rand(d, seed=11, scale=0.3), 1 + rand(d, seed=12, scale=0.3)
+    eps, theta = 2e-5, 12345.0
+    table = None
+    if rot:
+        half = rot // 2
+        inv = 1.0 / torch.pow(torch.tensor(theta), torch.arange(half, dtype=torch.float32) * 2.0 / rot)
+        ang = torch.arange(64, dtype=torch.float32)[:, None] * inv[None, :]
+        table = torch.stack((torch.cos(ang), torch.sin(ang)), -1).contiguous().to(DEV)
+    cache = torch.full((pages, 2, nkv, ps, d), 7.0, dtype=dtype, device=DEV)
+    dev = qkv.clone().to(DEV)
+    k.qk_norm_rope_kv_write(dev, positions.to(DEV), slots.to(DEV), qw.to(DEV), kw.to(DEV), eps, table, rot, cache,
+                            nq, nkv, d)
+    x = qkv.float()
+    q = P.rms_norm(x[:, :nq * d].view(T, nq, d), qw, eps)
+    kk = P.rms_norm(x[:, nq * d:(nq + nkv) * d].view(T, nkv, d), kw, eps)
+    v = x[:, (nq + nkv) * d:].view(T, nkv, d)
+    if rot:
+        cos, sin = P.rope_cos_sin(theta, rot, positions)
+        q, kk = P.apply_rope(q, cos, sin), P.apply_rope(kk, cos, sin)
+    close(dev[:, :nq * d], q.reshape(T, -1), TOL[dtype])
+    assert torch.equal(dev[:, nq * d:].cpu(), qkv[:, nq * d:])                       # k and v columns are left alone
+    got = cache.float().cpu()
+    touched = torch.zeros(pages, ps, dtype=torch.bool)
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        touched[s // ps, s % ps] = True
+        close(got[s // ps, 0, :, s % ps], kk[t], TOL[dtype])
+        close(got[s // ps, 1, :, s % ps], v[t], TOL[dtype] if dtype == torch.bfloat16 else 0.0)
+    mask = touched[:, None, None, :, None].expand_as(got)
+    assert bool((got[~mask] == 7.0).all())                                           # nothing else was written
+    # without norm weights and without a cache: queries are only rotated
+    dev2 = qkv.clone().to(DEV)
+    k.qk_norm_rope_kv_write(dev2, positions.to(DEV), None, None, None, eps, table, rot, None, nq, nkv, d)
+    q2 = x[:, :nq * d].view(T, nq, d)
+    if rot:
+        q2 = P.apply_rope(q2, cos, sin)
+    close(dev2[:, :nq * d], q2.reshape(T, -1), TOL[dtype])
+
+
+# ---- attention --------------------------------------------------------------------------------------------------
+
+def attention_case(dtype, nq, nkv, d, lens, new, page_size, seed, sharp=False):
+    """Requests with ``lens`` tokens in the cache, the last ``new`` of them being this step's queries."""
+    g = torch.Generator().manual_seed(seed)
+    ks, vs, qs = [], [], []
+    for n, m in zip(lens, new):
+        kd = torch.randn(n, nkv, d, generator=g)
+        vd = torch.randn(n, nkv, d, generator=g)
+        qd = torch.randn(m, nq, d, generator=g)
+        if sharp and n > 3:
+            # one far key per query head dominates: its value must come through almost alone
+            far = 1 if n < 40 else n // 7
+            for a in range(nq):
+                kd[far, a // (nq // nkv)] = qd[-1, a] / qd[-1, a].norm() * 6.0 * math.sqrt(d) / (nq // nkv + 1) * (a % (nq // nkv) + 1)
+        ks.append(kd.to(dtype).float()); vs.append(vd.to(dtype).float()); qs.append(qd.to(dtype).float())
+    pages = sum((n + page_size - 1) // page_size for n in lens) + 3
+    cache, tables = paged_cache(ks, vs, page_size, pages, seed + 1, dtype)
+    stride = max(len(t) for t in tables) + 2
+    bt = torch.full((len(lens), stride), -1, dtype=torch.int32)
+    for r, t in enumerate(tables):
+        bt[r, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    q_rows = torch.cat([q.reshape(q.shape[0], -1) for q in qs], 0)
+    # queries sit in the first nq*d columns of a wider row, as in a packed qkv row
+    wide = torch.cat([q_rows, torch.full((q_rows.shape[0], 2 * nkv * d), 99.0)], 1).to(dtype)
+    qsl = [0]
+    for m in new:
+        qsl.append(qsl[-1] + m)
+    treq = [r for r, m in enumerate(new) for _ in range(m)]
+    return dict(ks=ks, vs=vs, qs=qs, cache=cache, bt=bt, wide=wide, qsl=qsl, treq=treq)
+
+
+def attention_reference(case, lens, new, scale, window=None):
+    outs = []
+    for kd, vd, qd, n, m in zip(case["ks"], case["vs"], case["qs"], lens, new):
+        full_q = torch.zeros(n, qd.shape[1], qd.shape[2])
+        full_q[n - m:] = qd
+        outs.append(P.causal_attention(full_q, kd, vd, scale, window)[n - m:].reshape(m, -1))
+    return torch.cat(outs, 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq, nkv, d, ps", [(6, 3, 48, 16), (4, 1, 80, 5), (8, 2, 128, 32), (3, 3, 16, 1)])
+@pytest.mark.parametrize("window", [None, 9])
+def test_paged_attention_generic(dtype, nq, nkv, d, ps, window):
+    k = _k()
+    lens, new = [1, 37, 64, 130, 5], [1, 37, 1, 17, 2]
+    case = attention_case(dtype, nq, nkv, d, lens, new, ps, seed=20, sharp=True)
+    scale = 0.7 / math.sqrt(d)
+    T = sum(new)
+    out = torch.empty(T, nq * d, dtype=dtype, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    k.paged_attention_generic(case["wide"].to(DEV), out, case["cache"].to(DEV), case["bt"].to(DEV), i32(case["qsl"]),
+                              i32(lens), i32(case["treq"]), nq, nkv, d, scale, window or 0)
+    close(out, attention_reference(case, lens, new, scale, window), 2e-5 if dtype == torch.float32 else 1.5e-2)
+
+
+@pytest.mark.parametrize("nq, nkv, d, ps", [(16, 8, 128, 16), (8, 1, 64, 32), (12, 3, 128, 5), (32, 2, 256, 16),
+                                            (4, 4, 64, 16)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("window", [None, 50])
+def test_paged_attention_decode(nq, nkv, d, ps, splits, window):
+    k = _k()
+    assert k.paged_attention_decode_supports(d, nq, nkv)
+    lens = [1, 2, 15, 16, 17, 64, 333, 1000]
+    new = [1] * len(lens)
+    case = attention_case(torch.bfloat16, nq, nkv, d, lens, new, ps, seed=30, sharp=True)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.full((len(lens), nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    cache, bt, wide = case["cache"].to(DEV), case["bt"].to(DEV), case["wide"].to(DEV)
+    want = attention_reference(case, lens, new, scale, window)
+    for _ in range(2):                     # twice: the split counters must be left at zero
+        out.fill_(5.0)
+        k.paged_attention_decode(wide, out, cache, bt, sl, nq, nkv, d, scale, window or 0, splits)
+        close(out, want, 1.5e-2)
+    # the all-sizes kernel agrees on the same inputs
+    gen = torch.empty_like(out)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    k.paged_attention_generic(wide, gen, cache, bt, i32(case["qsl"]), sl, i32(case["treq"]), nq, nkv, d, scale, window or 0)
+    close(out, gen, 1.5e-2)
+
+
+def test_paged_attention_decode_refuses_other_sizes():
+    k = _k()
+    assert not k.paged_attention_decode_supports(48, 6, 3)
+    assert not k.paged_attention_decode_supports(128, 34, 2)
+    q = torch.zeros(1, 6 * 48 * 2, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(k.KernelError, match="not taken"):
+        k.paged_attention_decode(q, torch.zeros(1, 6 * 48, dtype=torch.bfloat16, device=DEV),
+                                 torch.zeros(2, 2, 3, 16, 48, dtype=torch.bfloat16, device=DEV),
+                                 torch.zeros(1, 2, dtype=torch.int32, device=DEV),
+                                 torch.ones(1, dtype=torch.int32, device=DEV), 6, 3, 48, 1.0, 0, 1)
+
+
+# ---- sampling ----------------------------------------------------------------------------------------------------
+
+def _sample(k, logits, rows):
+    import struct
+    raw = b"".join(struct.pack("<fiff", *r) for r in rows)
+    params = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(DEV)
+    out = torch.empty(len(rows), dtype=torch.int32, device=DEV)
+    k.sample(logits.to(DEV), params, out)
+    return out.cpu().tolist()
+
+
+@pytest.mark.parametrize("V", [517, 1000, 151936])
+def test_sampler_against_plain(V):
+    k = _k()
+    g = torch.Generator().manual_seed(40)
+    logits = torch.randn(6, V, generator=g) * 3
+    logits[1, 7] = logits[1, 400] = logits[1].max() + 1          # a tie for the maximum: the lowest id wins
+    rows = [(0.0, 0, 1.0, 0.5), (0.0, 0, 1.0, 0.9), (1.0, 1, 1.0, 0.3), (0.7, 40, 1.0, 0.77), (1.3, 0, 0.8, 0.41),
+            (0.9, 50, 0.9, 0.05)]
+    got = _sample(k, logits, rows)
+    want = [P.sample_plain(logits[i], *rows[i]) for i in range(6)]
+    assert got == want and got[1] == 7
+    # many draws of one row: same answers as the plain sampler for the same uniforms
+    row = logits[4:5].repeat(64, 1)
+    us = [(i + 0.5) / 64 for i in range(64)]
+    got = _sample(k, row, [(1.1, 30, 0.85, u) for u in us])
+    want = [P.sample_plain(logits[4], 1.1, 30, 0.85, u) for u in us]
+    assert sum(a != b for a, b in zip(got, want)) == 0
+    kth = torch.sort(logits[4], descending=True).values[29]
+    assert all(logits[4, t] >= kth for t in got)
