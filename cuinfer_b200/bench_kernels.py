@@ -1,0 +1,107 @@
+"""Micro-benchmarks of single kernels at model sizes: ``python -m cuinfer_b200.bench_kernels <kernel> [options]``.
+
+Each run builds inputs larger than the L2 cache (or rotates over several copies so that every launch reads cold
+data), times the kernel with CUDA events after warm-up and prints one JSON line with the achieved GB/s or
+TFLOP/s.  The same command under ``ncu`` gives the counters kept in ``profiles/``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+
+import torch
+
+from . import kernels
+
+
+def _time(fn, iters: int, warmup: int = 3) -> float:
+    """Milliseconds per call.  The calls are captured into one CUDA graph and the graph is replayed, so that
+    the figure is the device's time and not the time Python needs to issue a launch."""
+    for _ in range(warmup):
+        fn(0)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(iters):
+            fn(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / iters
+
+
+def attention_decode(args) -> dict:
+    R, ctx, nq, nkv, d, ps = args.batch, args.context, args.q_heads, args.kv_heads, args.head_dim, args.page_size
+    pages_per = (ctx + ps - 1) // ps
+    copies = max(1, args.copies)
+    num_pages = R * pages_per * copies
+    dev = "cuda:0"
+    cache = torch.randn(num_pages, 2, nkv, ps, d, device=dev, dtype=torch.bfloat16)
+    perm = torch.randperm(num_pages, device=dev).to(torch.int32).view(copies, R, pages_per)
+    q = torch.randn(R, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(R, nq * d, device=dev, dtype=torch.bfloat16)
+    sl = torch.full((R,), ctx, dtype=torch.int32, device=dev)
+    splits = args.splits or kernels.decode_splits(R, nkv, ctx)
+    scale = 1.0 / math.sqrt(d)
+
+    def run(i):
+        kernels.paged_attention_decode(q, out, cache, perm[i % copies], sl, nq, nkv, d, scale, 0, splits)
+
+    ms = _time(run, args.iters)
+    bytes_read = R * ctx * nkv * d * 2 * 2
+    return {"kernel": "paged_attention_decode", "batch": R, "context": ctx, "splits": splits, "ms": round(ms, 4),
+            "GBps": round(bytes_read / ms / 1e6, 1), "bytes": bytes_read}
+
+
+def gemm(args) -> dict:
+    from .parts.linear import matmul_nt
+
+    M, N, K = args.m, args.n, args.k
+    dev = "cuda:0"
+    copies = max(1, args.copies)
+    w = torch.randn(copies, N, K, device=dev, dtype=torch.bfloat16) * 0.02
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    out_dtype = torch.float32 if args.f32_out else torch.bfloat16
+
+    def run(i):
+        matmul_nt(x, w[i % copies], out_dtype)
+
+    ms = _time(run, args.iters)
+    return {"kernel": "matmul_nt", "M": M, "N": N, "K": K, "ms": round(ms, 4),
+            "GBps": round((N * K + M * K + M * N) * 2 / ms / 1e6, 1), "TFLOPs": round(2.0 * M * N * K / ms / 1e9, 2)}
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(prog="python -m cuinfer_b200.bench_kernels")
+    sub = p.add_subparsers(dest="kernel", required=True)
+    a = sub.add_parser("attention_decode")
+    a.add_argument("--batch", type=int, default=8)
+    a.add_argument("--context", type=int, default=4096)
+    a.add_argument("--q-heads", type=int, default=16)
+    a.add_argument("--kv-heads", type=int, default=8)
+    a.add_argument("--head-dim", type=int, default=128)
+    a.add_argument("--page-size", type=int, default=16)
+    a.add_argument("--splits", type=int, default=0)
+    a.add_argument("--copies", type=int, default=4, help="rotate over this many caches so that launches read cold data")
+    a.add_argument("--iters", type=int, default=20)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8)
+    g.add_argument("--n", type=int, default=4096)
+    g.add_argument("--k", type=int, default=1024)
+    g.add_argument("--f32-out", action="store_true")
+    g.add_argument("--copies", type=int, default=8)
+    g.add_argument("--iters", type=int, default=20)
+    args = p.parse_args(argv)
+    result = {"attention_decode": attention_decode, "gemm": gemm}[args.kernel](args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -32,26 +32,46 @@ template <int D>
 __device__ __forceinline__ void load_block(__nv_bfloat16* sK, __nv_bfloat16* sV, const __nv_bfloat16* cache,
                                            const int* table, int key0, int key_end, int page_size, int num_pages,
                                            int nkv, int kvh, int lane) {
-    constexpr int kChunks = D / 8;             // 16-byte chunks per row
-    const int row = lane >> 1;
-    const int half = lane & 1;
-    const int j = key0 + row;
-    bool valid = j < key_end;
-    int page = 0, off = 0;
-    if (valid) {
-        page = table[j / page_size];
-        off = j % page_size;
-        valid = page >= 0 && page < num_pages;
-    }
+    // Neighbouring lanes copy neighbouring 16-byte chunks of a row, so one instruction of the warp reads
+    // whole 128-byte lines: with D = 128 lanes 0-15 take one key row, lanes 16-31 the next.
+    constexpr int kChunks = D / 8;                               // 16-byte chunks per row
+    constexpr int kLanesPerRow = kChunks < 32 ? kChunks : 32;
+    constexpr int kRowsPerPass = 32 / kLanesPerRow;
+    constexpr int kPasses = kDecKeys / kRowsPerPass;
+    constexpr int kChunkPasses = kChunks / kLanesPerRow;         // > 1 only for D > 256
     const size_t head_stride = (size_t)page_size * D;
-    const __nv_bfloat16* kp = cache + (((size_t)(valid ? page : 0) * 2 + 0) * nkv + kvh) * head_stride + (size_t)off * D;
-    const __nv_bfloat16* vp = kp + (size_t)nkv * head_stride;
+    const int sub_row = lane / kLanesPerRow;
+    const int chunk0 = lane % kLanesPerRow;
+    // fast path: the whole block lies in one page
+    const int off0 = key0 % page_size;
+    const bool one_page = off0 + kDecKeys <= page_size;
+    int page0 = -1;
+    if (one_page && key0 < key_end) {
+        page0 = table[key0 / page_size];
+        if (page0 >= num_pages) page0 = -1;
+    }
 #pragma unroll
-    for (int c = 0; c < kChunks / 2; ++c) {
-        const int chunk = half * (kChunks / 2) + c;
-        const int sw = (chunk ^ (row & 7)) * 8;
-        cp_async16(sK + row * D + sw, kp + chunk * 8, valid);
-        cp_async16(sV + row * D + sw, vp + chunk * 8, valid);
+    for (int pass = 0; pass < kPasses; ++pass) {
+        const int row = pass * kRowsPerPass + sub_row;
+        const int j = key0 + row;
+        bool valid = j < key_end;
+        int page = page0, off = off0 + row;
+        if (!one_page && valid) {
+            page = table[j / page_size];
+            off = j % page_size;
+            if (page >= num_pages) page = -1;
+        }
+        valid = valid && page >= 0;
+        const __nv_bfloat16* kp = cache + (((size_t)(valid ? page : 0) * 2 + 0) * nkv + kvh) * head_stride +
+                                  (size_t)(valid ? off : 0) * D;
+        const __nv_bfloat16* vp = kp + (size_t)nkv * head_stride;
+#pragma unroll
+        for (int cp = 0; cp < kChunkPasses; ++cp) {
+            const int chunk = chunk0 + cp * kLanesPerRow;
+            const int sw = (chunk ^ (row & 7)) * 8;
+            cp_async16(sK + row * D + sw, kp + chunk * 8, valid);
+            cp_async16(sV + row * D + sw, vp + chunk * 8, valid);
+        }
     }
 }
 
@@ -262,21 +282,43 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // weights of the splits first (one parallel round of loads), then the weighted sums with several
+    // loads in flight per thread
     const size_t base = ((size_t)r * nkv + kvh) * splits;
+    float* sm_w = reinterpret_cast<float*>(smem_raw);            // [g][splits] weight of each split
+    float* sm_inv = sm_w + (size_t)g * splits;                    // [g] 1 / total
+    for (int idx = threadIdx.x; idx < g * splits; idx += blockDim.x) {
+        const int row = idx / splits, sp = idx - row * splits;
+        sm_w[idx] = __ldcg(&part_ml[((base + sp) * g + row) * 2]);
+    }
+    __syncthreads();
+    if (threadIdx.x < g) {
+        const int row = threadIdx.x;
+        float M = -INFINITY;
+        for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, sm_w[row * splits + sp]);
+        float L = 0.f;
+        for (int sp = 0; sp < splits; ++sp) {
+            const float ms = sm_w[row * splits + sp];
+            const float f = (ms == -INFINITY || M == -INFINITY) ? 0.f : exp2f(ms - M);
+            sm_w[row * splits + sp] = f;
+            L += __ldcg(&part_ml[((base + sp) * g + row) * 2 + 1]) * f;
+        }
+        sm_inv[row] = L > 0.f ? 1.f / L : 0.f;
+    }
+    __syncthreads();
     for (int idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
         const int row = idx / D, dim = idx - row * D;
-        float M = -INFINITY;
-        for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, __ldcg(&part_ml[((base + sp) * g + row) * 2]));
-        float L = 0.f, O = 0.f;
-        if (M != -INFINITY) {
-            for (int sp = 0; sp < splits; ++sp) {
-                const float ms = __ldcg(&part_ml[((base + sp) * g + row) * 2]);
-                const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-                L += __ldcg(&part_ml[((base + sp) * g + row) * 2 + 1]) * f;
-                O += __ldcg(&part_o[((base + sp) * g + row) * D + dim]) * f;
-            }
+        float O = 0.f;
+        int sp = 0;
+        for (; sp + 8 <= splits; sp += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(&part_o[((base + sp + u) * g + row) * D + dim]);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) O = fmaf(v[u], sm_w[row * splits + sp + u], O);
         }
-        out[(size_t)r * out_stride + (size_t)(kvh * g + row) * D + dim] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        for (; sp < splits; ++sp) O = fmaf(__ldcg(&part_o[((base + sp) * g + row) * D + dim]), sm_w[row * splits + sp], O);
+        out[(size_t)r * out_stride + (size_t)(kvh * g + row) * D + dim] = __float2bfloat16_rn(O * sm_inv[row]);
     }
     if (threadIdx.x == 0) counters[r * nkv + kvh] = 0;
 }
@@ -288,7 +330,9 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                          float* part_ml, int* counters, cudaStream_t stream) {
     const int g = nq / nkv;
     size_t smem = DecodeSmem<D>::kTotal;
-    const size_t merge = (size_t)(2 * kDecWarps * 16 + kDecWarps * g * D) * sizeof(float);
+    size_t merge = (size_t)(2 * kDecWarps * 16 + kDecWarps * g * D) * sizeof(float);
+    const size_t combine = (size_t)(g * splits + g) * sizeof(float);
+    if (combine > merge) merge = combine;
     if (merge > smem) smem = merge;
     static bool configured = false;
     if (!configured) {
@@ -334,7 +378,7 @@ extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out
     CIB_REQUIRE(cib_paged_attention_decode_supports(head_dim, nq, nkv),
                 "paged_attention_decode: head_dim %d with %d/%d heads is not taken by this kernel (64, 128 or 256; at most 16 query heads per kv head)",
                 head_dim, nq, nkv);
-    CIB_REQUIRE(num_requests >= 0 && splits >= 1 && splits <= 64, "paged_attention_decode: bad sizes R=%d splits=%d", num_requests, splits);
+    CIB_REQUIRE(num_requests >= 0 && splits >= 1 && splits <= 128, "paged_attention_decode: bad sizes R=%d splits=%d", num_requests, splits);
     CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0, "paged_attention_decode: bad cache geometry");
     CIB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4) == 0, "paged_attention_decode: q rows must be 4-byte aligned");
     CIB_REQUIRE(splits == 1 || (scratch && counters), "paged_attention_decode: splits need scratch and counters");

@@ -240,12 +240,25 @@ def paged_attention_decode_supports(head_dim: int, num_q_heads: int, num_kv_head
     return bool(library().cib_paged_attention_decode_supports(head_dim, num_q_heads, num_kv_heads))
 
 
-def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int:
-    """How many CTAs share the keys of one (request, kv head): enough CTAs to fill the 148 SMs about four
-    times over, but at least 64 keys each."""
-    want = -(-592 // max(1, num_requests * num_kv_heads))
-    by_len = max(1, max_seq_len // 64)
-    return max(1, min(32, want, by_len))
+def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots: int = 296) -> int:
+    """How many CTAs share the keys of one (request, kv head).
+
+    The GPU runs ``slots`` CTAs of this kernel at a time (two on each of the 148 SMs).  A launch's time is
+    estimated as (rounds of CTAs) x (keys per CTA + a fixed cost per CTA worth about 150 keys) + 11 key-times
+    per split for the combine; the constants were fitted to timings at batch 1, 8 and 64 with 4096 keys.
+    The number of splits with the smallest estimate wins, and a split never gets fewer than 64 keys.
+    """
+    pairs = max(1, num_requests * num_kv_heads)
+    best, best_cost = 1, None
+    for s in range(1, 65):
+        keys = -(-max_seq_len // s)
+        if s > 1 and keys < 64:
+            break
+        rounds = -(-pairs * s // slots)
+        cost = rounds * (keys + 150) + 11 * s
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
