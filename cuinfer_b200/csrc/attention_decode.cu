@@ -393,3 +393,82 @@ extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out
     }
     return -1;
 }
+
+// ---- the variant that allocates nothing (see attention_decode_static.h) --------------------------------------
+#include "attention_decode_static.h"
+
+#include <mutex>
+
+namespace cib {
+
+// Partial results of the splits, then the counters (as ints) behind them.  In host code this name is only a
+// stand-in for the symbol; the device address is looked up once per device below.
+static __device__ __align__(256) float g_static_decode_scratch[kStaticScratchFloats + kStaticCounters];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+// Device address of the array on the current device; looked up on the first call on that device.
+static int static_scratch_address(float** ptr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_error("paged_attention_decode_static: cannot tell the current device (%s)", cudaGetErrorString(e));
+        return -2;
+    }
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_static_decode_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_error("paged_attention_decode_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+            return -2;
+        }
+        g_static_scratch_ptr[dev] = p;
+    }
+    *ptr = g_static_scratch_ptr[dev];
+    return 0;
+}
+
+}  // namespace cib
+
+extern "C" int cib_paged_attention_decode_static(const void* q, int q_stride, void* out, int out_stride, const void* cache,
+                                                 int num_pages, int page_size, const int* block_table, int table_stride,
+                                                 const int* seq_lens, int num_requests, int nq, int nkv, int head_dim,
+                                                 float scale, int window, int splits, cudaStream_t stream) {
+    CIB_REQUIRE(cib_paged_attention_decode_supports(head_dim, nq, nkv),
+                "paged_attention_decode_static: head_dim %d with %d/%d heads is not taken by this kernel (64, 128 or 256; at most 16 query heads per kv head)",
+                head_dim, nq, nkv);
+    CIB_REQUIRE(num_requests >= 0 && splits >= 1 && splits <= 128, "paged_attention_decode_static: bad sizes R=%d splits=%d", num_requests, splits);
+    CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0, "paged_attention_decode_static: bad cache geometry");
+    CIB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4) == 0, "paged_attention_decode_static: q rows must be 4-byte aligned");
+    CIB_REQUIRE(num_requests <= 65535 && nkv <= 65535, "paged_attention_decode_static: grid too large");
+    const long long need = (long long)num_requests * nq * splits * (head_dim + 2);
+    CIB_REQUIRE(need <= (long long)kStaticScratchFloats,
+                "paged_attention_decode_static: %d requests x %d heads x %d splits x head_dim %d need %lld floats of scratch, the built-in array holds %d; use fewer splits or cib_paged_attention_decode with a buffer of your own",
+                num_requests, nq, splits, head_dim, need, (int)kStaticScratchFloats);
+    CIB_REQUIRE((long long)num_requests * nkv <= (long long)kStaticCounters,
+                "paged_attention_decode_static: %d requests x %d kv heads exceed the %d built-in counters",
+                num_requests, nkv, (int)kStaticCounters);
+    if (num_requests == 0) return 0;
+    float* base = nullptr;
+    if (static_scratch_address(&base) != 0) return -2;
+    float* part_o = base;
+    float* part_ml = base + (size_t)num_requests * nq * splits * head_dim;
+    int* counters = reinterpret_cast<int*>(base + kStaticScratchFloats);
+    if (splits > 1) {
+        // the array keeps the last call's contents: the counters must start at zero
+        cudaError_t e = cudaMemsetAsync(counters, 0, sizeof(int) * (size_t)num_requests * nkv, stream);
+        if (e != cudaSuccess) {
+            set_error("paged_attention_decode_static: clearing the counters failed: %s", cudaGetErrorString(e));
+            return -2;
+        }
+    }
+    switch (head_dim) {
+        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream);
+        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream);
+        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream);
+    }
+    return -1;
+}
