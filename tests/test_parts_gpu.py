@@ -1,0 +1,300 @@
+"""Each kind of part alone, and models put together from parts in ways the built-in architecture does not use:
+a windowed attention with partial rotary width and no q/k norm, a layer that runs twice with the second run
+reading the first run's cache, and a toy mixer with per-request state that is defined here, registered, built and
+stepped without touching the framework's files.  All are replayed whole, in portions and mixed, and compared
+with plain restatements written in this file from ``plain_qwen3``'s functions.
+"""
+from __future__ import annotations
+
+import math
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+import traces
+from conftest import TOLERANCE, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+H, V, MAXPOS = 48, 211, 400
+
+
+def _register(name, spec_fn):
+    from cuinfer_b200.config import register_architecture
+    register_architecture(name, lambda raw: SimpleNamespace(**raw), spec_fn, replace=True)
+
+
+def _base_cfg(name, **kw):
+    return dict(architectures=[name], hidden_size=H, vocab_size=V, max_position_embeddings=MAXPOS, **kw)
+
+
+def _model_spec(cfg, layers, **kw):
+    from cuinfer_b200.parts import ModelSpec, PartSpec
+    return ModelSpec(hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, max_positions=cfg.max_position_embeddings,
+                     layers=tuple(layers), final_norm=PartSpec("rmsnorm", eps=cfg.eps), lm_head_name="lm_head.weight", **kw)
+
+
+def _replay_all(folder, dtype, requests, tmp_path, plain_fn, block=16):
+    """whole / tail / portions / mixed with page reuse, each against ``plain_fn(ids) -> logits``."""
+    worst = 0.0
+    for label, steps in [("whole", traces.whole(requests)), ("tail", traces.tail_decode(requests, 20)),
+                         ("portions", traces.portions(requests)), ("mixed", traces.mixed(requests, max_live=3))]:
+        out = str(tmp_path / f"{label}_{dtype}")
+        traces.replay_in_process(folder, dtype, steps, out, traces.live_token_peak(steps), block)
+        got = traces.collect(steps, out, V)
+        for rid, toks in requests.items():
+            ref = plain_fn(list(toks)).numpy()
+            scale = float(np.abs(ref).max())
+            for pos, row in sorted(got[rid].items()):
+                err = float(np.abs(row - ref[pos]).max()) / scale
+                worst = max(worst, err)
+                assert err <= TOLERANCE[dtype], f"{label}: request {rid} first wrong position {pos} (error {err:.3e})"
+    return worst
+
+
+# ---- 1. windowed attention, partial rotary width, no q/k norm, custom scale ------------------------------------
+
+WINDOW, ROT, NQ, NKV, D, SCALE = 21, 8, 4, 2, 24, 0.31
+
+
+def _window_spec(cfg):
+    from cuinfer_b200.parts import LayerSpec, PartSpec
+    pos = PartSpec("rope_neox", theta=cfg.theta, rotary_dim=ROT, max_positions=cfg.max_position_embeddings)
+    mixer = PartSpec("attention", name="attn", num_heads=NQ, num_kv_heads=NKV, head_dim=D, qk_norm=False,
+                     scale=SCALE, window=WINDOW, position=pos)
+    layer = lambda i: LayerSpec(prefix=f"blk.{i}", block=PartSpec("prenorm", norm_names=("n1", "n2")), mixer=mixer,
+                                feed_forward=PartSpec("swiglu", name="ff", intermediate_size=72),
+                                norm=PartSpec("rmsnorm", eps=cfg.eps))
+    return _model_spec(cfg, [layer(0), layer(1)])
+
+
+def _window_plain(cfg, w, ids):
+    x = P.embed(w["model.embed_tokens.weight"], ids)
+    n = len(ids)
+    pos = torch.arange(n)
+    cos, sin = P.rope_cos_sin(cfg["theta"], ROT, pos)
+    for i in range(2):
+        p = f"blk.{i}"
+        h = P.rms_norm(x, w[f"{p}.n1.weight"], cfg["eps"])
+        q = P.apply_rope((h @ w[f"{p}.attn.q_proj.weight"].T).view(n, NQ, D), cos, sin)
+        k = P.apply_rope((h @ w[f"{p}.attn.k_proj.weight"].T).view(n, NKV, D), cos, sin)
+        v = (h @ w[f"{p}.attn.v_proj.weight"].T).view(n, NKV, D)
+        x = x + P.causal_attention(q, k, v, SCALE, WINDOW).reshape(n, -1) @ w[f"{p}.attn.o_proj.weight"].T
+        x = x + P.swiglu(P.rms_norm(x, w[f"{p}.n2.weight"], cfg["eps"]), w, f"{p}.ff")
+    return P.rms_norm(x, w["model.norm.weight"], cfg["eps"]) @ w["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_attention_with_partial_rotary(dtype, tmp_path):
+    from cuinfer_b200.engine import replay
+    from cuinfer_b200.weights import write_random_model
+
+    _register("ToyWindowLM", _window_spec)
+    cfg = _base_cfg("ToyWindowLM", theta=5000.0, eps=1e-5)
+    folder = write_random_model(str(tmp_path / "m"), cfg, 3, std=0.08 if dtype == "float32" else 0.05, gain_std=0.1,
+                                dtype=dtype)
+    pcfg, w = P.load_folder(folder)
+    requests = {f"r{i}": random_tokens(V, n, 300 + i) for i, n in enumerate([70, 45, 100, 33])}
+    _replay_all(folder, dtype, requests, tmp_path, lambda ids: _window_plain(pcfg, w, ids))
+    # the windowed group gives pages back while a request is still running
+    runner = replay.make_runner(folder, dtype, 256, 16)
+    assert runner.groups[0].window == WINDOW
+    runner.reserve("a", 100)
+    from cuinfer_b200.engine import StepEntry
+    runner.step([StepEntry("a", requests["r2"], [99])])
+    table = runner.manager.block_table("a", 0)
+    assert table[0] == -1 and table[3] == -1 and table[-1] >= 0 and sum(p >= 0 for p in table) <= 3
+
+
+# ---- 2. one layer run twice; the second run reads the first run's cache ------------------------------------------
+
+def _twice_spec(cfg):
+    from cuinfer_b200.parts import LayerSpec, PartSpec
+    pos = PartSpec("rope_neox", theta=cfg.theta, rotary_dim=16, max_positions=cfg.max_position_embeddings)
+    mixer = PartSpec("attention", name="attn", num_heads=3, num_kv_heads=1, head_dim=16, qk_norm=True,
+                     qk_norm_eps=cfg.eps, position=pos)
+    layer = LayerSpec(prefix="blk.0", block=PartSpec("prenorm", norm_names=("n1", "n2")), mixer=mixer,
+                      feed_forward=PartSpec("swiglu", name="ff", intermediate_size=40), norm=PartSpec("rmsnorm", eps=cfg.eps))
+    return _model_spec(cfg, [layer], order=(0, 0), cache_source={1: 0})
+
+
+def _twice_plain(cfg, w, ids):
+    x = P.embed(w["model.embed_tokens.weight"], ids)
+    n = len(ids)
+    cos, sin = P.rope_cos_sin(cfg["theta"], 16, torch.arange(n))
+    p = "blk.0"
+    kept = None
+    for run in range(2):
+        h = P.rms_norm(x, w[f"{p}.n1.weight"], cfg["eps"])
+        q = (h @ w[f"{p}.attn.q_proj.weight"].T).view(n, 3, 16)
+        q = P.apply_rope(P.rms_norm(q, w[f"{p}.attn.q_norm.weight"], cfg["eps"]), cos, sin)
+        if run == 0:
+            k = (h @ w[f"{p}.attn.k_proj.weight"].T).view(n, 1, 16)
+            k = P.apply_rope(P.rms_norm(k, w[f"{p}.attn.k_norm.weight"], cfg["eps"]), cos, sin)
+            v = (h @ w[f"{p}.attn.v_proj.weight"].T).view(n, 1, 16)
+            kept = (k, v)
+        k, v = kept                                   # the second run attends over the first run's keys and values
+        x = x + P.causal_attention(q, k, v, 0.25).reshape(n, -1) @ w[f"{p}.attn.o_proj.weight"].T
+        x = x + P.swiglu(P.rms_norm(x, w[f"{p}.n2.weight"], cfg["eps"]), w, f"{p}.ff")
+    return P.rms_norm(x, w["model.norm.weight"], cfg["eps"]) @ w["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_run_twice_sharing_a_cache(dtype, tmp_path):
+    from cuinfer_b200.engine import replay
+    from cuinfer_b200.weights import write_random_model
+
+    _register("ToyTwiceLM", _twice_spec)
+    cfg = _base_cfg("ToyTwiceLM", theta=10000.0, eps=1e-6)
+    folder = write_random_model(str(tmp_path / "m"), cfg, 4, std=0.08 if dtype == "float32" else 0.05, dtype=dtype)
+    pcfg, w = P.load_folder(folder)
+    requests = {f"r{i}": random_tokens(V, n, 400 + i) for i, n in enumerate([50, 81, 37])}
+    _replay_all(folder, dtype, requests, tmp_path, lambda ids: _twice_plain(pcfg, w, ids))
+    runner = replay.make_runner(folder, dtype, 64, 16)
+    assert len(runner.groups) == 1 and runner.groups[0].runs == (0,)          # one cache for two runs
+    assert [t.name for t in runner.model.tensors()].count("blk.0.attn.q_proj.weight") == 1
+
+
+# ---- 3. a toy mixer with state of its own ---------------------------------------------------------------------------
+
+def _define_toy_mixer():
+    from cuinfer_b200.parts import MIXERS, Mixer, StateNeed, TensorSpec
+
+    if "running_mean" in MIXERS:
+        return
+
+    @MIXERS.register("running_mean")
+    class RunningMean(Mixer):
+        """y_t = W · mean(x_0 .. x_t).  Per-request state: the running sum of x and the count, 32-bit."""
+
+        def tensors(self):
+            return [TensorSpec(f"{self.prefix}.proj.weight", (self.hidden_size, self.hidden_size))]
+
+        def load(self, store):
+            self.weight = store.get(self.tensors()[0]).float()
+
+        def state_need(self):
+            return StateNeed((self.hidden_size + 1,), "float32")
+
+        def forward(self, x, ctx, run):
+            state = ctx.run_state(run)
+            out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            starts = ctx.query_start_loc_host
+            for r, slot in enumerate(ctx.state_slots_host):
+                rows = x[starts[r]:starts[r + 1]].float()
+                sums = torch.cumsum(rows, 0) + state[slot, :-1]
+                counts = state[slot, -1] + torch.arange(1, rows.shape[0] + 1, device=x.device, dtype=torch.float32)
+                out[starts[r]:starts[r + 1]] = sums / counts[:, None]
+                state[slot, :-1] = sums[-1]
+                state[slot, -1] = counts[-1]
+            return (out @ self.weight.T).to(x.dtype)
+
+
+def _toy_spec(cfg):
+    from cuinfer_b200.parts import LayerSpec, PartSpec
+    _define_toy_mixer()
+    pos = PartSpec("rope_neox", theta=cfg.theta, rotary_dim=16, max_positions=cfg.max_position_embeddings)
+    attn = PartSpec("attention", name="attn", num_heads=2, num_kv_heads=2, head_dim=16, qk_norm=True, qk_norm_eps=cfg.eps,
+                    position=pos)
+    block = PartSpec("prenorm", norm_names=("n1", "n2"))
+    ff = PartSpec("swiglu", name="ff", intermediate_size=56)
+    norm = PartSpec("rmsnorm", eps=cfg.eps)
+    return _model_spec(cfg, [
+        LayerSpec("blk.0", block, PartSpec("running_mean", name="mean"), ff, norm),      # state, no pages
+        LayerSpec("blk.1", block, attn, ff, norm),                                       # pages, no state
+        LayerSpec("blk.2", block, PartSpec("running_mean", name="mean"), ff, norm),
+    ])
+
+
+def _toy_plain(cfg, w, ids):
+    x = P.embed(w["model.embed_tokens.weight"], ids)
+    n = len(ids)
+    cos, sin = P.rope_cos_sin(cfg["theta"], 16, torch.arange(n))
+    for i in range(3):
+        p = f"blk.{i}"
+        h = P.rms_norm(x, w[f"{p}.n1.weight"], cfg["eps"])
+        if i != 1:
+            mean = torch.cumsum(h, 0) / torch.arange(1, n + 1, dtype=torch.float32)[:, None]
+            x = x + mean @ w[f"{p}.mean.proj.weight"].T
+        else:
+            q = (h @ w[f"{p}.attn.q_proj.weight"].T).view(n, 2, 16)
+            k = (h @ w[f"{p}.attn.k_proj.weight"].T).view(n, 2, 16)
+            v = (h @ w[f"{p}.attn.v_proj.weight"].T).view(n, 2, 16)
+            q = P.apply_rope(P.rms_norm(q, w[f"{p}.attn.q_norm.weight"], cfg["eps"]), cos, sin)
+            k = P.apply_rope(P.rms_norm(k, w[f"{p}.attn.k_norm.weight"], cfg["eps"]), cos, sin)
+            x = x + P.causal_attention(q, k, v, 0.25).reshape(n, -1) @ w[f"{p}.attn.o_proj.weight"].T
+        x = x + P.swiglu(P.rms_norm(x, w[f"{p}.n2.weight"], cfg["eps"]), w, f"{p}.ff")
+    return P.rms_norm(x, w["model.norm.weight"], cfg["eps"]) @ w["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_registers_builds_and_steps(dtype, tmp_path):
+    from cuinfer_b200.engine import replay
+    from cuinfer_b200.weights import write_random_model
+
+    _register("ToyStateLM", _toy_spec)
+    cfg = _base_cfg("ToyStateLM", theta=10000.0, eps=1e-6)
+    folder = write_random_model(str(tmp_path / "m"), cfg, 5, std=0.08 if dtype == "float32" else 0.05, dtype=dtype)
+    pcfg, w = P.load_folder(folder)
+    # more requests than live slots, so that state slots are used again and must start from zero
+    requests = {f"r{i}": random_tokens(V, n, 500 + i) for i, n in enumerate([40, 23, 66, 31, 52])}
+    _replay_all(folder, dtype, requests, tmp_path, lambda ids: _toy_plain(pcfg, w, ids))
+    runner = replay.make_runner(folder, dtype, 128, 16)
+    assert sorted(runner.storage.state) == [0, 2] and runner.storage.state[0].shape == (8, H + 1)
+    assert [g.runs for g in runner.groups] == [(1,)]
+
+
+# ---- 4. single parts against their formulas ---------------------------------------------------------------------------
+
+class DictStore:
+    def __init__(self, tensors, device="cuda:0"):
+        self.tensors, self.device = tensors, torch.device(device)
+
+    def get(self, spec):
+        return self.tensors[spec.name].to(self.device)
+
+    def get_stacked(self, specs):
+        return torch.cat([self.get(s) for s in specs], 0).contiguous()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_feed_forward_and_position_parts_alone(dtype):
+    from cuinfer_b200.parts import FEED_FORWARDS, NORMS, POSITION_ENCODINGS, PartSpec, ResidualStream
+
+    g = torch.Generator().manual_seed(7)
+    hid, inter, rows = 88, 136, 9
+    tol = 2e-6 if dtype == torch.float32 else 1.5e-2
+    # norm: folds the pending delta into the residual, then normalises
+    norm = NORMS.get("rmsnorm")(PartSpec("rmsnorm", eps=2e-5), hidden_size=hid, prefix="n", dtype=dtype)
+    assert [(t.name, t.shape, t.init) for t in norm.tensors()] == [("n.weight", (hid,), "ones")]
+    gain = 1 + 0.2 * torch.randn(hid, generator=g)
+    norm.load(DictStore({"n.weight": gain}))
+    res, delta = torch.randn(rows, hid, generator=g), torch.randn(rows, hid, generator=g).to(dtype)
+    stream = ResidualStream(res.clone().cuda(), delta.cuda())
+    out = norm.add_norm(stream)
+    assert stream.pending is None and out.dtype == dtype
+    want_res = res + delta.float()
+    assert float((stream.residual.cpu() - want_res).abs().max()) < 1e-6
+    want = P.rms_norm(want_res, gain, 2e-5)
+    assert float((out.float().cpu() - want).abs().max()) / float(want.abs().max()) < tol
+    # feed-forward
+    ff = FEED_FORWARDS.get("swiglu")(PartSpec("swiglu", intermediate_size=inter), hidden_size=hid, prefix="ff", dtype=dtype)
+    assert sorted(t.name for t in ff.tensors()) == ["ff.down_proj.weight", "ff.gate_proj.weight", "ff.up_proj.weight"]
+    wts = {n: (0.2 * torch.randn(s, generator=g)).to(dtype) for n, s in
+           [("ff.gate_proj.weight", (inter, hid)), ("ff.up_proj.weight", (inter, hid)), ("ff.down_proj.weight", (hid, inter))]}
+    ff.load(DictStore(wts))
+    x = torch.randn(rows, hid, generator=g).to(dtype)
+    got = ff.forward(x.cuda(), None)
+    want = P.swiglu(x.float(), {k: v.float() for k, v in wts.items()}, "ff")
+    assert float((got.float().cpu() - want).abs().max()) / float(want.abs().max()) < (1e-5 if dtype == torch.float32 else 2e-2)
+    # rotary table: 32-bit angles, (cos, sin) pairs
+    rope = POSITION_ENCODINGS.get("rope_neox")(PartSpec("rope_neox", theta=777.0, rotary_dim=12, max_positions=50),
+                                               hidden_size=hid, prefix="", dtype=dtype)
+    rope.load(DictStore({}))
+    cos, sin = P.rope_cos_sin(777.0, 12, torch.arange(50))
+    table = rope.table().cpu()
+    assert table.shape == (50, 6, 2) and torch.equal(table[..., 0], cos) and torch.equal(table[..., 1], sin)
+    assert POSITION_ENCODINGS.get("none")(PartSpec("none"), hidden_size=hid, prefix="", dtype=dtype).table() is None
