@@ -59,6 +59,29 @@ def attention_decode(args) -> dict:
             "GBps": round(bytes_read / ms / 1e6, 1), "bytes": bytes_read}
 
 
+def attention_prefill(args) -> dict:
+    """One request of ``--tokens`` new tokens after ``--prefix`` cached ones."""
+    n, prefix, nq, nkv, d, ps = args.tokens, args.prefix, args.q_heads, args.kv_heads, args.head_dim, args.page_size
+    total = n + prefix
+    pages = (total + ps - 1) // ps
+    dev = "cuda:0"
+    cache = torch.randn(pages, 2, nkv, ps, d, device=dev, dtype=torch.bfloat16)
+    table = torch.randperm(pages, device=dev).to(torch.int32).view(1, pages)
+    q = torch.randn(n, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(n, nq * d, device=dev, dtype=torch.bfloat16)
+    qsl = torch.tensor([0, n], dtype=torch.int32, device=dev)
+    sl = torch.tensor([total], dtype=torch.int32, device=dev)
+    scale = 1.0 / math.sqrt(d)
+
+    def run(i):
+        kernels.paged_attention_prefill(q, out, cache, table, qsl, sl, [n], nq, nkv, d, scale, 0)
+
+    ms = _time(run, args.iters)
+    flops = 4.0 * nq * d * (n * prefix + n * (n + 1) / 2.0)
+    return {"kernel": "paged_attention_prefill", "tokens": n, "prefix": prefix, "ms": round(ms, 4),
+            "TFLOPs": round(flops / ms / 1e9, 1)}
+
+
 def gemm(args) -> dict:
     from .parts.linear import matmul_nt
 
@@ -90,6 +113,14 @@ def main(argv=None) -> int:
     a.add_argument("--splits", type=int, default=0)
     a.add_argument("--copies", type=int, default=4, help="rotate over this many caches so that launches read cold data")
     a.add_argument("--iters", type=int, default=20)
+    f = sub.add_parser("attention_prefill")
+    f.add_argument("--tokens", type=int, default=2048)
+    f.add_argument("--prefix", type=int, default=0)
+    f.add_argument("--q-heads", type=int, default=16)
+    f.add_argument("--kv-heads", type=int, default=8)
+    f.add_argument("--head-dim", type=int, default=128)
+    f.add_argument("--page-size", type=int, default=16)
+    f.add_argument("--iters", type=int, default=10)
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=8)
     g.add_argument("--n", type=int, default=4096)
@@ -98,7 +129,7 @@ def main(argv=None) -> int:
     g.add_argument("--copies", type=int, default=8)
     g.add_argument("--iters", type=int, default=20)
     args = p.parse_args(argv)
-    result = {"attention_decode": attention_decode, "gemm": gemm}[args.kernel](args)
+    result = {"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm}[args.kernel](args)
     print(json.dumps(result))
     return 0
 

@@ -70,6 +70,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_qk_norm_rope_kv_write": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
         "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
+        "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
         "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
     }
@@ -79,6 +80,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn.restype = _I
     lib.cib_paged_attention_decode_supports.argtypes = [_I, _I, _I]
     lib.cib_paged_attention_decode_supports.restype = _I
+    lib.cib_paged_attention_prefill_supports.argtypes = [_I, _I, _I]
+    lib.cib_paged_attention_prefill_supports.restype = _I
     lib.cib_paged_attention_decode_scratch_floats.argtypes = [_I, _I, _I, _I]
     lib.cib_paged_attention_decode_scratch_floats.restype = ctypes.c_longlong
 
@@ -293,6 +296,32 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
         float(scale), int(window), int(splits), scratch.data_ptr() if scratch is not None else None,
         counters.data_ptr() if counters is not None else None, _stream())
     _check(rc, "paged_attention_decode")
+    _count()
+
+
+def paged_attention_prefill_supports(head_dim: int, num_q_heads: int, num_kv_heads: int) -> bool:
+    return bool(library().cib_paged_attention_prefill_supports(head_dim, num_q_heads, num_kv_heads))
+
+
+def paged_attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                            query_start_loc: torch.Tensor, seq_lens: torch.Tensor, query_lens_host, num_q_heads: int,
+                            num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """bfloat16 tensor-core attention for any mix of prompt portions and decoded tokens.
+    ``query_lens_host``: tokens each request brings in this step (host ints), to size the grid."""
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("paged_attention_prefill: bfloat16 only")
+    if q.stride(1) != 1 or out.stride(1) != 1 or out.shape != (T, num_q_heads * head_dim):
+        raise KernelError("paged_attention_prefill: q/out rows must be dense and out [T, nq*d]")
+    g = num_q_heads // num_kv_heads
+    tiles = sum((n * g + 63) // 64 for n in query_lens_host)
+    rc = library().cib_paged_attention_prefill(
+        _cuda(q, "q", contiguous=False), q.stride(0), _cuda(out, "out", contiguous=False), out.stride(0),
+        _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
+        block_table.stride(0), _cuda(query_start_loc, "query_start_loc", torch.int32),
+        _cuda(seq_lens, "seq_lens", torch.int32), len(query_lens_host), tiles, num_q_heads, num_kv_heads, head_dim,
+        float(scale), int(window), _stream())
+    _check(rc, "paged_attention_prefill")
     _count()
 
 

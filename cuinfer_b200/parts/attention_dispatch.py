@@ -19,6 +19,12 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: Step
         kernels.paged_attention_decode(qkv, out, kv.cache, kv.group.block_table, ctx.seq_lens, num_heads,
                                        num_kv_heads, head_dim, scale, window, splits)
         return
+    if qkv.dtype == torch.bfloat16 and kernels.paged_attention_prefill_supports(head_dim, num_heads, num_kv_heads):
+        starts = ctx.query_start_loc_host
+        lens = [starts[i + 1] - starts[i] for i in range(ctx.num_requests)]
+        kernels.paged_attention_prefill(qkv, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
+                                        lens, num_heads, num_kv_heads, head_dim, scale, window)
+        return
     kernels.paged_attention_generic(
         qkv, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens, ctx.token_request,
         num_heads, num_kv_heads, head_dim, scale, window)

@@ -269,6 +269,25 @@ def test_paged_attention_decode(nq, nkv, d, ps, splits, window):
     close(out, gen, 1.5e-2)
 
 
+@pytest.mark.parametrize("nq, nkv, d, ps", [(16, 8, 128, 16), (8, 1, 64, 32), (12, 4, 128, 5), (6, 6, 64, 16)])
+@pytest.mark.parametrize("window", [None, 40])
+def test_paged_attention_prefill(nq, nkv, d, ps, window):
+    """Portions of every length beside decoded tokens: tiles that end inside a request, cross the diagonal,
+    start at a late position, and a far key that dominates."""
+    k = _k()
+    assert k.paged_attention_prefill_supports(d, nq, nkv)
+    lens = [1, 37, 64, 130, 5, 300, 257, 1000]
+    new = [1, 37, 1, 17, 2, 300, 129, 1]
+    case = attention_case(torch.bfloat16, nq, nkv, d, lens, new, ps, seed=60, sharp=True)
+    scale = 1.0 / math.sqrt(d)
+    T = sum(new)
+    out = torch.full((T, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    k.paged_attention_prefill(case["wide"].to(DEV), out, case["cache"].to(DEV), case["bt"].to(DEV), i32(case["qsl"]),
+                              i32(lens), new, nq, nkv, d, scale, window or 0)
+    close(out, attention_reference(case, lens, new, scale, window), 1.5e-2)
+
+
 def test_paged_attention_decode_refuses_other_sizes():
     k = _k()
     assert not k.paged_attention_decode_supports(48, 6, 3)
