@@ -91,6 +91,7 @@ def gemm(args) -> dict:
     w = torch.randn(copies, N, K, device=dev, dtype=torch.bfloat16) * 0.02
     x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
     out_dtype = torch.float32 if args.f32_out else torch.bfloat16
+    kernels.use_pdl = bool(args.pdl)
 
     def run(i):
         matmul_nt(x, w[i % copies], out_dtype)
@@ -126,6 +127,7 @@ def main(argv=None) -> int:
     g.add_argument("--n", type=int, default=4096)
     g.add_argument("--k", type=int, default=1024)
     g.add_argument("--f32-out", action="store_true")
+    g.add_argument("--pdl", action="store_true", help="launch with programmatic dependent launch")
     g.add_argument("--copies", type=int, default=8)
     g.add_argument("--iters", type=int, default=20)
     args = p.parse_args(argv)

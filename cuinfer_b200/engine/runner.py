@@ -14,6 +14,8 @@ tool does that); the step records the stored tokens afterwards.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -355,7 +357,7 @@ class DecodeGraph:
     """
 
     def __init__(self, runner: "ModelRunner", rows: int, table_stride: int) -> None:
-        self.runner = runner
+        self._runner = weakref.ref(runner)       # no cycle: a dropped engine frees its graphs at once
         self.rows = rows
         self.stride = table_stride
         G = len(runner.groups)
@@ -383,6 +385,13 @@ class DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_replay = 0
+
+    @property
+    def runner(self) -> "ModelRunner":
+        runner = self._runner()
+        if runner is None:
+            raise RuntimeError("the engine of this decode graph is gone")
+        return runner
 
     def _view(self, host: np.ndarray, name: str) -> np.ndarray:
         off, n = self.layout[name]
@@ -472,8 +481,11 @@ class DecodeGraph:
         self._forward()
         self.kernels_per_replay = kernels.launch_count - before
         torch.cuda.synchronize(self.runner.device)
+        # Destroying another graph (an engine dropped earlier, collected just now) is an error inside a capture
+        # in the default mode and would invalidate this one: collect garbage first and capture in relaxed mode.
+        gc.collect()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, capture_error_mode="relaxed"):
             self.logits = self._forward()
         torch.cuda.synchronize(self.runner.device)
 

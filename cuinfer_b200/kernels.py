@@ -9,6 +9,7 @@ cannot be built or loaded, or a tensor is not on a CUDA device, the call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Optional
 
@@ -71,6 +72,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
         "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
         "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+        "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
         "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
     }
@@ -80,6 +82,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn.restype = _I
     lib.cib_paged_attention_decode_supports.argtypes = [_I, _I, _I]
     lib.cib_paged_attention_decode_supports.restype = _I
+    lib.cib_gemm_skinny_supports.argtypes = [_I, _I, _I, _I]
+    lib.cib_gemm_skinny_supports.restype = _I
     lib.cib_paged_attention_prefill_supports.argtypes = [_I, _I, _I]
     lib.cib_paged_attention_prefill_supports.restype = _I
     lib.cib_paged_attention_decode_scratch_floats.argtypes = [_I, _I, _I, _I]
@@ -339,6 +343,70 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         _cuda(a, "a", contiguous=False), a.stride(0), _cuda(w, "w", contiguous=False), w.stride(0), _code(a, "a"),
         _cuda(out, "out", contiguous=False), out.stride(0), _code(out, "out"), M, N, K, _stream())
     _check(rc, "gemm_generic")
+    _count()
+
+
+# Programmatic dependent launch for the kernels that support it: such a kernel may start, and prefetch its
+# weights, while the kernel before it in the stream is still running; it reads that kernel's results only after
+# `griddepcontrol.wait`.  CUINFER_B200_PDL=0 switches it off.
+use_pdl = os.environ.get("CUINFER_B200_PDL", "1") != "0"
+
+EPILOGUE_BF16, EPILOGUE_F32, EPILOGUE_SILU_PAIR = 0, 1, 2
+
+
+def gemm_skinny_supports(M: int, N: int, K: int, with_norm: bool = False) -> bool:
+    return bool(library().cib_gemm_skinny_supports(M, N, K, 1 if with_norm else 0))
+
+
+def gemm_skinny(w: torch.Tensor, out: torch.Tensor, *, act: torch.Tensor | None = None,
+                residual: torch.Tensor | None = None, pending: torch.Tensor | None = None,
+                norm_weight: torch.Tensor | None = None, eps: float = 0.0, residual_out: torch.Tensor | None = None,
+                silu_pair: bool = False) -> None:
+    """out = act @ w^T for at most 16 rows, bfloat16 weights.
+
+    Either ``act`` [M, K] is given, or ``residual`` (float32 [M, K]) with optional ``pending``: then the rows are
+    RMSNorm(residual + pending) * norm_weight, computed in the kernel, and ``residual_out`` (another buffer)
+    receives residual + pending.  ``silu_pair``: ``w`` is [2I, K] = gates then ups and out [M, I] = silu(g) * u.
+    ``out`` float32 selects the 32-bit store."""
+    N, K = w.shape
+    M = out.shape[0]
+    if w.dtype != torch.bfloat16 or w.stride(1) != 1:
+        raise KernelError("gemm_skinny: weights must be bfloat16 with dense rows")
+    if silu_pair:
+        epi = EPILOGUE_SILU_PAIR
+        if out.dtype != torch.bfloat16 or out.shape[1] * 2 != N:
+            raise KernelError("gemm_skinny: a gate/up pair writes bfloat16 [M, N/2]")
+    else:
+        if out.shape[1] != N:
+            raise KernelError(f"gemm_skinny: out must be [M, {N}]")
+        epi = EPILOGUE_F32 if out.dtype == torch.float32 else EPILOGUE_BF16
+        if out.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError("gemm_skinny: out must be bfloat16 or float32")
+    if out.stride(1) != 1:
+        raise KernelError("gemm_skinny: out rows must be dense")
+    if act is not None:
+        if act.dtype != torch.bfloat16 or act.shape != (M, K) or act.stride(1) != 1:
+            raise KernelError("gemm_skinny: act must be bfloat16 [M, K] with dense rows")
+    else:
+        if residual is None or residual.dtype != torch.float32 or residual.shape != (M, K) or not residual.is_contiguous():
+            raise KernelError("gemm_skinny: residual must be contiguous float32 [M, K]")
+        if pending is not None and (pending.shape != (M, K) or not pending.is_contiguous()):
+            raise KernelError("gemm_skinny: pending must be contiguous [M, K]")
+        if norm_weight is None or norm_weight.numel() != K:
+            raise KernelError("gemm_skinny: the norm needs K weights")
+        if residual_out is not None and (residual_out.shape != (M, K) or residual_out.dtype != torch.float32
+                                         or residual_out.data_ptr() == residual.data_ptr()):
+            raise KernelError("gemm_skinny: residual_out must be another float32 [M, K] buffer")
+    rc = library().cib_gemm_skinny(
+        _cuda(w, "w", contiguous=False), w.stride(0), N, K,
+        _cuda(act, "act", contiguous=False) if act is not None else None, act.stride(0) if act is not None else 0,
+        _cuda(residual, "residual") if residual is not None else None,
+        _cuda(pending, "pending") if pending is not None else None, _code(pending, "pending") if pending is not None else 0,
+        _cuda(norm_weight, "norm_weight") if norm_weight is not None else None,
+        _code(norm_weight, "norm_weight") if norm_weight is not None else 0, float(eps),
+        _cuda(residual_out, "residual_out") if residual_out is not None else None,
+        _cuda(out, "out", contiguous=False), out.stride(0), M, epi, N // 2 if silu_pair else 0, 1 if use_pdl else 0, _stream())
+    _check(rc, "gemm_skinny")
     _count()
 
 

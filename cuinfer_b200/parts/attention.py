@@ -27,6 +27,8 @@ from .spec import PagedCacheNeed, PartSpec, TensorSpec
 
 @MIXERS.register("attention")
 class PagedAttention(Mixer):
+    accepts_lazy_norm = True       # the q/k/v projection can compute the norm of its input itself
+
     def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
         super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
         self.num_heads = int(spec.num_heads)
@@ -85,7 +87,7 @@ class PagedAttention(Mixer):
             self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps,
             self.position.table(), self.position.rotary_dim,
             kv.cache if kv.writes else None, self.num_heads, self.num_kv_heads, self.head_dim)
-        out = torch.empty((x.shape[0], self.q_size), dtype=x.dtype, device=x.device)
+        out = torch.empty((qkv.shape[0], self.q_size), dtype=qkv.dtype, device=qkv.device)
         attention_dispatch.paged_attention(qkv, out, kv, ctx, self.num_heads, self.num_kv_heads, self.head_dim,
                                            self.scale, self.window)
         return self.o.forward(out)

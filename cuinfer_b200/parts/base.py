@@ -31,11 +31,48 @@ class ResidualStream:
     residual and the normalisation in one pass.
     """
 
-    __slots__ = ("residual", "pending")
+    __slots__ = ("residual", "pending", "_spare")
 
     def __init__(self, residual: torch.Tensor, pending: Optional[torch.Tensor] = None) -> None:
         self.residual = residual
         self.pending = pending
+        self._spare: Optional[torch.Tensor] = None
+
+    def spare(self) -> torch.Tensor:
+        """A second buffer of the residual's shape, for kernels that write the new residual beside the old."""
+        if self._spare is None:
+            self._spare = torch.empty_like(self.residual)
+        return self._spare
+
+    def swap(self) -> None:
+        """The spare buffer now holds the residual (and no delta is pending any more)."""
+        self.residual, self._spare = self._spare, self.residual
+        self.pending = None
+
+
+class LazyNorm:
+    """A norm of the residual stream that has not been computed yet.
+
+    A block hands this to a mixer or feed-forward that declares ``accepts_lazy_norm``; its first projection
+    may then compute the norm inside its own kernel (and fold the pending delta into the residual there).
+    ``materialize()`` gives the normed rows as a tensor, whatever happened before.
+    """
+
+    __slots__ = ("stream", "norm", "_rows")
+
+    def __init__(self, stream: ResidualStream, norm: "Norm") -> None:
+        self.stream = stream
+        self.norm = norm
+        self._rows: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return self.stream.residual.shape
+
+    def materialize(self) -> torch.Tensor:
+        if self._rows is None:
+            self._rows = self.norm.add_norm(self.stream)     # folds a pending delta if there still is one
+        return self._rows
 
 
 class Part:

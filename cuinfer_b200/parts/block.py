@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from typing import Callable, List
 
-from .base import Block, FeedForward, Mixer, Norm, Part, ResidualStream
+from .base import Block, FeedForward, LazyNorm, Mixer, Norm, Part, ResidualStream
 from .context import StepContext
 from .registry import BLOCKS
 from .spec import PartSpec
@@ -29,7 +29,15 @@ class PreNormBlock(Block):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
     def forward(self, stream: ResidualStream, ctx: StepContext, run: int) -> None:
-        h = self.mixer_norm.add_norm(stream)
+        h = self._normed(stream, self.mixer_norm, self.mixer)
         stream.pending = self.mixer.forward(h, ctx, run)
-        h = self.feed_forward_norm.add_norm(stream)
+        h = self._normed(stream, self.feed_forward_norm, self.feed_forward)
         stream.pending = self.feed_forward.forward(h, ctx)
+
+    @staticmethod
+    def _normed(stream: ResidualStream, norm: Norm, consumer: Part):
+        """The normed rows for ``consumer``: computed now, or handed over uncomputed when the consumer can
+        fold the norm into its first projection."""
+        if getattr(consumer, "accepts_lazy_norm", False):
+            return LazyNorm(stream, norm)
+        return norm.add_norm(stream)

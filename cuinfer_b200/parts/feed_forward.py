@@ -20,6 +20,8 @@ from .spec import PartSpec, TensorSpec
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
+    accepts_lazy_norm = True       # the gate/up projection can compute the norm of its input itself
+
     def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
         super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
         self.intermediate_size = int(spec.intermediate_size)
@@ -36,7 +38,5 @@ class SwiGLU(FeedForward):
         self.down.load(store)
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gate_up = self.gate_up.forward(x)
-        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.silu_mul(gate_up, act)
+        act = self.gate_up.forward(x, silu_pair=True)       # silu(gate) * up, fused where the kernel allows
         return self.down.forward(act)

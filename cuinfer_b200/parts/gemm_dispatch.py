@@ -15,6 +15,9 @@ def bf16_matmul_nt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     """out[M, N] = x[M, K] @ weight[N, K]^T; x and weight bfloat16, out bfloat16 or float32."""
     M, K = x.shape
     N = weight.shape[0]
+    if M <= 16 and weight.is_contiguous() and kernels.gemm_skinny_supports(M, N, K):
+        kernels.gemm_skinny(weight, out, act=x)
+        return
     if K % 8 == 0 and N % 8 == 0 and x.is_contiguous() and weight.is_contiguous():
         if out.dtype == torch.bfloat16:
             torch.mm(x, weight.t(), out=out)

@@ -16,6 +16,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from .. import kernels
+from .base import LazyNorm
 from .spec import TensorSpec
 
 
@@ -60,7 +61,56 @@ class Linear:
             raise ValueError(f"tied weight has shape {list(weight.shape)}")
         self.weight = weight
 
-    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def forward(self, x, out_dtype: Optional[torch.dtype] = None, silu_pair: bool = False) -> torch.Tensor:
+        """``x`` is a tensor [M, K] or a :class:`LazyNorm`.  ``silu_pair``: the weight is gates then ups and the
+        result is ``silu(gate) * up`` [M, N/2]."""
         if self.weight is None:
             raise RuntimeError(f"projection {self.names} used before its weights were loaded")
-        return matmul_nt(x, self.weight, out_dtype)
+        fused = self._forward_skinny(x, out_dtype, silu_pair)
+        if fused is not None:
+            return fused
+        if isinstance(x, LazyNorm):
+            x = x.materialize()
+        y = matmul_nt(x, self.weight, out_dtype if not silu_pair else None)
+        if not silu_pair:
+            return y
+        act = torch.empty((y.shape[0], y.shape[1] // 2), dtype=y.dtype, device=y.device)
+        kernels.silu_mul(y, act)
+        return act
+
+    def _forward_skinny(self, x, out_dtype, silu_pair) -> Optional[torch.Tensor]:
+        """The few-rows kernel with the norm in its prologue and/or the gate in its epilogue, when it takes
+        the shape; None otherwise."""
+        w = self.weight
+        if w.dtype != torch.bfloat16 or not w.is_contiguous():
+            return None
+        lazy = isinstance(x, LazyNorm)
+        M = x.shape[0]
+        N, K = w.shape
+        if M == 0 or M > 16:
+            return None
+        out_dtype = out_dtype or torch.bfloat16
+        if silu_pair and out_dtype != torch.bfloat16:
+            return None
+        out_cols = N // 2 if silu_pair else N
+        if lazy and x._rows is None:
+            from .norm import RMSNorm
+            norm, stream = x.norm, x.stream
+            if (type(norm) is RMSNorm and norm.weight is not None and stream.residual.is_contiguous()
+                    and kernels.gemm_skinny_supports(M, N, K, True)
+                    and (stream.pending is None or stream.pending.is_contiguous())):
+                out = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
+                has_delta = stream.pending is not None
+                kernels.gemm_skinny(w, out, residual=stream.residual, pending=stream.pending, norm_weight=norm.weight,
+                                    eps=norm.eps, residual_out=stream.spare() if has_delta else None, silu_pair=silu_pair)
+                if has_delta:
+                    stream.swap()
+                return out
+        rows = x.materialize() if lazy else x
+        if rows.dtype != torch.bfloat16 or rows.stride(1) != 1 or not kernels.gemm_skinny_supports(M, N, K, False):
+            return None
+        if not silu_pair and not lazy:
+            return None          # the plain case goes through matmul_nt, which picks the same kernel
+        out = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
+        kernels.gemm_skinny(w, out, act=rows, silu_pair=silu_pair)
+        return out

@@ -116,6 +116,69 @@ def test_gemm_generic(M, N, K, dtypes):
     assert torch.equal(one[0].cpu(), out[M // 2].cpu())
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N, K", [(1024, 1024), (48, 96), (1000, 2048), (3000, 72), (151936, 1024)])
+def test_gemm_skinny(M, N, K):
+    k = _k()
+    assert k.gemm_skinny_supports(M, N, K)
+    a, w = rand(M, K, seed=13, dtype=torch.bfloat16), rand(N, K, seed=14, scale=0.05, dtype=torch.bfloat16)
+    want = a.double() @ w.double().T
+    wd, ad = w.to(DEV), a.to(DEV)
+    for dtype, tol in ((torch.bfloat16, 6e-3), (torch.float32, 2e-5)):
+        out = torch.full((M, N), 7.0, dtype=dtype, device=DEV)
+        k.gemm_skinny(wd, out, act=ad)
+        close(out, want, tol)
+    # a row's result does not depend on how many rows are beside it
+    one = torch.empty(1, N, dtype=torch.float32, device=DEV)
+    k.gemm_skinny(wd, one, act=ad[M - 1:M])
+    full = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    k.gemm_skinny(wd, full, act=ad)
+    assert torch.equal(one[0].cpu(), full[M - 1].cpu())
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("H, I", [(1024, 3072), (96, 320), (80, 176)])
+@pytest.mark.parametrize("pending_dtype", [None, torch.bfloat16, torch.float32])
+def test_gemm_skinny_with_norm_and_gated_epilogue(M, H, I, pending_dtype):
+    k = _k()
+    if not k.gemm_skinny_supports(M, 2 * I, H, True):
+        pytest.skip("shape not taken")
+    res = rand(M, H, seed=15, scale=2.0)
+    pend = None if pending_dtype is None else rand(M, H, seed=16, dtype=pending_dtype)
+    gain = (1 + rand(H, seed=17, scale=0.2)).to(torch.bfloat16)
+    w = rand(2 * I, H, seed=18, scale=0.05, dtype=torch.bfloat16)
+    eps = 1e-5
+    x = res + (pend.float() if pend is not None else 0)
+    normed = P.rms_norm(x, gain.float(), eps).to(torch.bfloat16).float()
+    gu = normed.double() @ w.double().T
+    # norm prologue, plain store
+    res_out = torch.zeros(M, H, dtype=torch.float32, device=DEV)
+    out = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+    k.gemm_skinny(w.to(DEV), out, residual=res.to(DEV), pending=pend.to(DEV) if pend is not None else None,
+                  norm_weight=gain.to(DEV), eps=eps, residual_out=res_out)
+    close(out, gu, 8e-3)
+    close(res_out, x, 1e-7)
+    # norm prologue and gated epilogue together
+    act = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    k.gemm_skinny(w.to(DEV), act, residual=res.to(DEV), pending=pend.to(DEV) if pend is not None else None,
+                  norm_weight=gain.to(DEV), eps=eps, residual_out=res_out, silu_pair=True)
+    g, u = gu[:, :I], gu[:, I:]
+    close(act, g / (1 + torch.exp(-g)) * u, 1e-2)
+    # gated epilogue on plain activations
+    act2 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    k.gemm_skinny(w.to(DEV), act2, act=normed.to(torch.bfloat16).to(DEV), silu_pair=True)
+    close(act2, g / (1 + torch.exp(-g)) * u, 1e-2)
+
+
+def test_gemm_skinny_refuses_other_shapes():
+    k = _k()
+    assert not k.gemm_skinny_supports(17, 64, 64) and not k.gemm_skinny_supports(4, 64, 60)
+    assert not k.gemm_skinny_supports(16, 64, 16384) and not k.gemm_skinny_supports(16, 64, 4096, True)
+    with pytest.raises(k.KernelError, match="not taken"):
+        k.gemm_skinny(torch.zeros(64, 60, dtype=torch.bfloat16, device=DEV), torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV),
+                      act=torch.zeros(4, 60, dtype=torch.bfloat16, device=DEV))
+
+
 # ---- q/k norm + rotary + cache write ------------------------------------------------------------------------
 
 def paged_cache(k_dense, v_dense, page_size, num_pages, seed, dtype):
