@@ -99,20 +99,6 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int k_end = min(seq_len, k_begin + chunk);
     const int* table = block_table + (size_t)r * table_stride;
 
-    // ---- query fragments: rows 0..g-1 are the heads of this kv head, the rest are zero ----
-    uint32_t qf[D / 16][4];
-    {
-        const __nv_bfloat16* qp = q + (size_t)r * q_stride + (size_t)kvh * g * D;
-#pragma unroll
-        for (int kt = 0; kt < D / 16; ++kt) {
-            const int c0 = kt * 16 + quad * 2;
-            qf[kt][0] = qrow < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)qrow * D + c0) : 0u;
-            qf[kt][1] = qrow + 8 < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)(qrow + 8) * D + c0) : 0u;
-            qf[kt][2] = qrow < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)qrow * D + c0 + 8) : 0u;
-            qf[kt][3] = qrow + 8 < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)(qrow + 8) * D + c0 + 8) : 0u;
-        }
-    }
-
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
@@ -127,11 +113,41 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int my_blocks = total_blocks > warp ? (total_blocks - warp + kDecWarps - 1) / kDecWarps : 0;
     auto block_key = [&](int i) { return k_begin + (i * kDecWarps + warp) * kDecKeys; };
 
+    // Keys and values of earlier steps do not depend on the kernel before this one: their first blocks are
+    // requested before `griddepcontrol.wait`.  Only the block that holds this step's own token (position
+    // seq_len - 1, written by the kernel before) has to wait; so do the queries.
+    griddep_launch();
+    int deferred = -1;
 #pragma unroll
     for (int s = 0; s < kDecStages - 1; ++s) {
-        if (s < my_blocks) load_block<D>(stage_k(s), stage_v(s), cache, table, block_key(s), k_end, page_size, num_pages, nkv, kvh, lane);
+        if (s < my_blocks) {
+            if (block_key(s) + kDecKeys > pos) deferred = s;
+            else load_block<D>(stage_k(s), stage_v(s), cache, table, block_key(s), k_end, page_size, num_pages, nkv, kvh, lane);
+        }
         cp_async_commit();
     }
+    griddep_wait();
+    if (deferred >= 0) {
+        // one warp per (request, kv head): its late block is its own commit group, so let everything land first
+        // and the loop's group counting starts clean
+        load_block<D>(stage_k(deferred), stage_v(deferred), cache, table, block_key(deferred), k_end, page_size, num_pages, nkv, kvh, lane);
+        cp_async_commit();
+        cp_async_wait<0>();
+    }
+    // ---- query fragments: rows 0..g-1 are the heads of this kv head, the rest are zero ----
+    uint32_t qf[D / 16][4];
+    {
+        const __nv_bfloat16* qp = q + (size_t)r * q_stride + (size_t)kvh * g * D;
+#pragma unroll
+        for (int kt = 0; kt < D / 16; ++kt) {
+            const int c0 = kt * 16 + quad * 2;
+            qf[kt][0] = qrow < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)qrow * D + c0) : 0u;
+            qf[kt][1] = qrow + 8 < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)(qrow + 8) * D + c0) : 0u;
+            qf[kt][2] = qrow < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)qrow * D + c0 + 8) : 0u;
+            qf[kt][3] = qrow + 8 < g ? *reinterpret_cast<const uint32_t*>(qp + (size_t)(qrow + 8) * D + c0 + 8) : 0u;
+        }
+    }
+
     for (int i = 0; i < my_blocks; ++i) {
         cp_async_wait<kDecStages - 2>();
         __syncwarp();
@@ -327,7 +343,7 @@ template <int D>
 static int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* cache, int num_pages,
                          int page_size, const int* block_table, int table_stride, const int* seq_lens,
                          int num_requests, int nq, int nkv, float scale, int window, int splits, float* part_o,
-                         float* part_ml, int* counters, cudaStream_t stream) {
+                         float* part_ml, int* counters, cudaStream_t stream, bool use_pdl = false) {
     const int g = nq / nkv;
     size_t smem = DecodeSmem<D>::kTotal;
     size_t merge = (size_t)(2 * kDecWarps * 16 + kDecWarps * g * D) * sizeof(float);
@@ -346,10 +362,14 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     CIB_REQUIRE(smem <= 200 * 1024, "paged_attention_decode: needs %zu bytes of shared memory", smem);
     dim3 grid(splits, nkv, num_requests);
     const float scale_log2 = scale * 1.4426950408889634f;
-    paged_attention_decode_kernel<D><<<grid, kDecWarps * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache, num_pages,
-        page_size, block_table, table_stride, seq_lens, nq, nkv, scale_log2, window, splits, part_o, part_ml, counters);
-    CIB_LAUNCH_CHECK("paged_attention_decode");
+    cudaError_t e = launch_pdl(paged_attention_decode_kernel<D>, grid, dim3(kDecWarps * 32), smem, stream, use_pdl,
+                               (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+                               (const __nv_bfloat16*)cache, num_pages, page_size, block_table, table_stride, seq_lens, nq,
+                               nkv, scale_log2, window, splits, part_o, part_ml, counters);
+    if (e != cudaSuccess) {
+        set_error("paged_attention_decode: launch failed: %s", cudaGetErrorString(e));
+        return -2;
+    }
     return 0;
 }
 
@@ -374,7 +394,7 @@ extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out
                                           int num_pages, int page_size, const int* block_table, int table_stride,
                                           const int* seq_lens, int num_requests, int nq, int nkv, int head_dim,
                                           float scale, int window, int splits, float* scratch, int* counters,
-                                          cudaStream_t stream) {
+                                          int use_pdl, cudaStream_t stream) {
     CIB_REQUIRE(cib_paged_attention_decode_supports(head_dim, nq, nkv),
                 "paged_attention_decode: head_dim %d with %d/%d heads is not taken by this kernel (64, 128 or 256; at most 16 query heads per kv head)",
                 head_dim, nq, nkv);
@@ -387,9 +407,9 @@ extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_requests * nq * splits * head_dim : nullptr;
     switch (head_dim) {
-        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream);
-        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream);
-        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream);
+        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0);
+        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0);
+        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0);
     }
     return -1;
 }

@@ -37,9 +37,6 @@ struct SkinnyArgs {
     int act_stride;                                          // shared-memory row stride in elements
 };
 
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -98,34 +95,63 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     // ---- activations -> shared memory (bfloat16 rows, padded), optionally normalised on the way ----
     const int rows_pad = MT * 8;
     if (a.res_in != nullptr) {
+        float* s_x = reinterpret_cast<float*>(s_red);               // un-normalised 32-bit rows [rows][K]
         for (int row = warp; row < rows_pad; row += kSkWarps) {
             float ss = 0.f;
             if (row < a.M) {
                 const float* rp = a.res_in + (size_t)row * a.K;
-                for (int k = lane * 4; k < a.K; k += 128) {
-                    float4 x = *reinterpret_cast<const float4*>(rp + k);
+                // eight independent 16-byte loads of the residual (and of the delta) are in flight per lane
+                for (int k0 = lane * 4; k0 < a.K; k0 += 128 * 8) {
+                    float4 x[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int k = k0 + u * 128;
+                        x[u] = k < a.K ? *reinterpret_cast<const float4*>(rp + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
                     if (a.pending) {
                         if (a.pending_bf16) {
-                            const uint2 pv = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.pending) + (size_t)row * a.K + k);
-                            const __nv_bfloat162 p01 = *reinterpret_cast<const __nv_bfloat162*>(&pv.x);
-                            const __nv_bfloat162 p23 = *reinterpret_cast<const __nv_bfloat162*>(&pv.y);
-                            x.x += __low2float(p01); x.y += __high2float(p01); x.z += __low2float(p23); x.w += __high2float(p23);
+                            uint2 pv[8];
+                            const __nv_bfloat16* pp = reinterpret_cast<const __nv_bfloat16*>(a.pending) + (size_t)row * a.K;
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const int k = k0 + u * 128;
+                                pv[u] = k < a.K ? *reinterpret_cast<const uint2*>(pp + k) : make_uint2(0u, 0u);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const __nv_bfloat162 p01 = *reinterpret_cast<const __nv_bfloat162*>(&pv[u].x);
+                                const __nv_bfloat162 p23 = *reinterpret_cast<const __nv_bfloat162*>(&pv[u].y);
+                                x[u].x += __low2float(p01); x[u].y += __high2float(p01);
+                                x[u].z += __low2float(p23); x[u].w += __high2float(p23);
+                            }
                         } else {
-                            const float4 pv = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.pending) + (size_t)row * a.K + k);
-                            x.x += pv.x; x.y += pv.y; x.z += pv.z; x.w += pv.w;
+                            const float* pp = reinterpret_cast<const float*>(a.pending) + (size_t)row * a.K;
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const int k = k0 + u * 128;
+                                if (k < a.K) {
+                                    const float4 pv = *reinterpret_cast<const float4*>(pp + k);
+                                    x[u].x += pv.x; x[u].y += pv.y; x[u].z += pv.z; x[u].w += pv.w;
+                                }
+                            }
                         }
                     }
-                    ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
-                    if (tile_block == 0 && a.res_out) *reinterpret_cast<float4*>(a.res_out + (size_t)row * a.K + k) = x;
-                    // keep the un-normalised sum in shared memory for the second pass (as 32-bit, two slots per value)
-                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(s_red) + (size_t)row * a.K + k) = x;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int k = k0 + u * 128;
+                        if (k < a.K) {
+                            ss += x[u].x * x[u].x + x[u].y * x[u].y + x[u].z * x[u].z + x[u].w * x[u].w;
+                            if (tile_block == 0 && a.res_out) *reinterpret_cast<float4*>(a.res_out + (size_t)row * a.K + k) = x[u];
+                            *reinterpret_cast<float4*>(s_x + (size_t)row * a.K + k) = x[u];
+                        }
+                    }
                 }
                 ss = warp_sum(ss);
             }
             const float factor = row < a.M ? rsqrtf(ss / (float)a.K + a.eps) : 0.f;
             __syncwarp();
             for (int k = lane * 4; k < a.K; k += 128) {
-                float4 x = row < a.M ? *reinterpret_cast<const float4*>(reinterpret_cast<float*>(s_red) + (size_t)row * a.K + k)
+                float4 x = row < a.M ? *reinterpret_cast<const float4*>(s_x + (size_t)row * a.K + k)
                                      : make_float4(0.f, 0.f, 0.f, 0.f);
                 const float n0 = x.x * factor * a.norm_w[k], n1 = x.y * factor * a.norm_w[k + 1];
                 const float n2 = x.z * factor * a.norm_w[k + 2], n3 = x.w * factor * a.norm_w[k + 3];

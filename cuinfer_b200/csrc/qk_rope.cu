@@ -10,7 +10,7 @@
 //
 // Row layout: [num_q_heads * d | num_kv_heads * d (keys) | num_kv_heads * d (values)].
 // Cache layout of one layer: [page][0 = keys, 1 = values][kv head][slot in page][d].
-#include "common.cuh"
+#include "mma_utils.cuh"
 
 namespace cib {
 
@@ -25,6 +25,8 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int row_stride
                                              int max_positions, T* __restrict__ cache, int num_pages,
                                              int page_size, int nq, int nkv, int d, int write_cache) {
     extern __shared__ float smem[];
+    griddep_launch();
+    griddep_wait();          // the rows come from the projection before this kernel
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int head = blockIdx.y * kRopeWarps + warp;
@@ -90,7 +92,7 @@ extern "C" int cib_qk_norm_rope_kv_write(void* qkv, int dtype, int row_stride, c
                                          const void* k_weight, int weight_dtype, int has_norm, float eps,
                                          const float* rope_table, int rotary_dim, int max_positions,
                                          void* cache, int num_pages, int page_size, int num_tokens, int nq,
-                                         int nkv, int d, int write_cache, cudaStream_t stream) {
+                                         int nkv, int d, int write_cache, int use_pdl, cudaStream_t stream) {
     CIB_REQUIRE(num_tokens >= 0 && nq > 0 && nkv > 0 && d > 0, "qk_norm_rope: bad sizes T=%d nq=%d nkv=%d d=%d",
                 num_tokens, nq, nkv, d);
     CIB_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0,
@@ -106,17 +108,21 @@ extern "C" int cib_qk_norm_rope_kv_write(void* qkv, int dtype, int row_stride, c
     dim3 grid(num_tokens, (heads + kRopeWarps - 1) / kRopeWarps);
     const size_t smem = (size_t)kRopeWarps * d * sizeof(float);
     AnyVec qw{q_weight, weight_dtype == kBF16}, kw{k_weight, weight_dtype == kBF16};
+    cudaError_t e;
     if (dtype == kF32) {
-        qk_norm_rope_kv_write_kernel<float><<<grid, kRopeWarps * 32, smem, stream>>>(
-            (float*)qkv, row_stride, positions, slot_mapping, qw, kw, has_norm, eps, rope_table, rotary_dim,
-            max_positions, (float*)cache, num_pages, page_size, nq, nkv, d, write_cache);
+        e = launch_pdl(qk_norm_rope_kv_write_kernel<float>, grid, dim3(kRopeWarps * 32), smem, stream, use_pdl != 0,
+                       (float*)qkv, row_stride, positions, slot_mapping, qw, kw, has_norm, eps, rope_table, rotary_dim,
+                       max_positions, (float*)cache, num_pages, page_size, nq, nkv, d, write_cache);
     } else if (dtype == kBF16) {
-        qk_norm_rope_kv_write_kernel<__nv_bfloat16><<<grid, kRopeWarps * 32, smem, stream>>>(
-            (__nv_bfloat16*)qkv, row_stride, positions, slot_mapping, qw, kw, has_norm, eps, rope_table,
-            rotary_dim, max_positions, (__nv_bfloat16*)cache, num_pages, page_size, nq, nkv, d, write_cache);
+        e = launch_pdl(qk_norm_rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(kRopeWarps * 32), smem, stream, use_pdl != 0,
+                       (__nv_bfloat16*)qkv, row_stride, positions, slot_mapping, qw, kw, has_norm, eps, rope_table,
+                       rotary_dim, max_positions, (__nv_bfloat16*)cache, num_pages, page_size, nq, nkv, d, write_cache);
     } else {
         CIB_REQUIRE(false, "qk_norm_rope: unsupported dtype %d", dtype);
     }
-    CIB_LAUNCH_CHECK("qk_norm_rope_kv_write");
+    if (e != cudaSuccess) {
+        set_error("qk_norm_rope_kv_write: launch failed: %s", cudaGetErrorString(e));
+        return -2;
+    }
     return 0;
 }

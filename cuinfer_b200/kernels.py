@@ -68,9 +68,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_add_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
         "cib_gather_rows": [_P, _P, _I, _P, _P, _I, _I, _I, _P],
         "cib_silu_mul": [_P, _P, _I, _I, _I, _P],
-        "cib_qk_norm_rope_kv_write": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "cib_qk_norm_rope_kv_write": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
-        "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
+        "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P],
         "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
@@ -214,7 +214,8 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mappi
         _cuda(rope_table, "rope_table", torch.float32) if rope_table is not None else None,
         rotary_dim if rope_table is not None else 0, rope_table.shape[0] if rope_table is not None else 0,
         _cuda(cache, "cache") if write_cache else None, cache.shape[0] if write_cache else 0,
-        cache.shape[3] if write_cache else 0, T, num_q_heads, num_kv_heads, head_dim, 1 if write_cache else 0, _stream())
+        cache.shape[3] if write_cache else 0, T, num_q_heads, num_kv_heads, head_dim, 1 if write_cache else 0,
+        1 if use_pdl else 0, _stream())
     _check(rc, "qk_norm_rope_kv_write")
     _count()
 
@@ -298,7 +299,7 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
         _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
         block_table.stride(0), _cuda(seq_lens, "seq_lens", torch.int32), R, num_q_heads, num_kv_heads, head_dim,
         float(scale), int(window), int(splits), scratch.data_ptr() if scratch is not None else None,
-        counters.data_ptr() if counters is not None else None, _stream())
+        counters.data_ptr() if counters is not None else None, 1 if use_pdl else 0, _stream())
     _check(rc, "paged_attention_decode")
     _count()
 
