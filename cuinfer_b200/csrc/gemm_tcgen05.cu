@@ -1,0 +1,312 @@
+// out[M, N] = a[M, K] · w[N, K]^T in bfloat16 on the 5th-generation tensor cores: TMA-fed, TMEM-accumulated.
+//
+// The reference calls cuBLAS for every projection (csrc/ops/projection.cu:32-44).  This is the prompt-sized
+// replacement (many rows): one 128 x BN output tile per CTA, K walked in 64-element steps.
+//
+//   warp 0, one thread : TMA producer.  Per step two `cp.async.bulk.tensor.2d` loads (an activation tile 128 x 64 and
+//                        a weight tile BN x 64, both K-major, 128-byte swizzle) into a ring of shared-memory stages,
+//                        completion counted in bytes on the stage's "full" mbarrier.  No multicast.
+//   warp 1, one thread : MMA issuer.  Waits for "full", issues four `tcgen05.mma.cta_group::1.kind::f16`
+//                        (128 x BN x 16 each) whose accumulator lives in tensor memory, then `tcgen05.commit` to the
+//                        stage's "empty" mbarrier; after the last step a commit to the "accumulator ready" mbarrier.
+//   warps 2-5          : epilogue.  Each warp owns the 32 TMEM lanes (= output rows) its rank allows, reads them with
+//                        `tcgen05.ld.32x32b`, converts and stores rows to global memory (bfloat16 or float32).
+//
+// Rows beyond M, features beyond N and the tail of K read as zeros (TMA out-of-bounds fill) and are not stored.
+// Every mbarrier wait is bounded: if a limit is hit the kernel raises a flag in global memory, stops issuing,
+// drains what it started, frees its tensor memory and returns, so a fault in this kernel cannot hang the device.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace cib {
+
+constexpr int kTcBM = 128;
+constexpr int kTcBK = 64;
+constexpr long long kTcWaitCycles = 2000000000ll;      // about a second: far beyond any wait of a healthy run
+
+__device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(tc_smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the limit was hit (the caller raises the error flag and leaves).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (clock64() - start < kTcWaitCycles) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(tc_smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows 128 bytes apart inside an 8-row
+// atom, atoms 1024 bytes apart; descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc_k_major_sw128(const void* smem) {
+    uint64_t d = 0;
+    d |= (uint64_t)((tc_smem_u32(smem) & 0x3ffff) >> 4);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                 // version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D = F32, A = B = BF16, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BN, int STAGES>
+struct TcSmem {
+    static constexpr int kABytes = kTcBM * kTcBK * 2;
+    static constexpr int kBBytes = BN * kTcBK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTotal = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN, int STAGES, bool F32OUT>
+__global__ void __launch_bounds__(192)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    void* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ error_flag) {
+    extern __shared__ unsigned char smem_raw[];
+    // stages must start on a 1024-byte boundary (one swizzle atom)
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * TcSmem<BN, STAGES>::kStageBytes);
+    uint64_t* full = bars;                 // [STAGES]
+    uint64_t* empty = bars + STAGES;       // [STAGES]
+    uint64_t* acc_ready = bars + 2 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * kTcBM, n0 = blockIdx.x * BN;
+    const int k_steps = (K + kTcBK - 1) / kTcBK;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            for (int kb = 0; kb < k_steps; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t phase = (kb / STAGES) & 1;
+                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 1); s_abort = 1; break; }
+                if (*(volatile int*)&s_abort) break;
+                unsigned char* a_dst = tiles + (size_t)s * TcSmem<BN, STAGES>::kStageBytes;
+                unsigned char* b_dst = a_dst + TcSmem<BN, STAGES>::kABytes;
+                mbar_expect_tx(&full[s], TcSmem<BN, STAGES>::kStageBytes);
+                tma_load_2d(a_dst, &map_a, &full[s], kb * kTcBK, m0);
+                tma_load_2d(b_dst, &map_w, &full[s], kb * kTcBK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            constexpr uint32_t idesc = umma_idesc_bf16(kTcBM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < k_steps && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t phase = (kb / STAGES) & 1;
+                if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 2); s_abort = 1; ok = false; break; }
+                tcgen05_fence_after();
+                const unsigned char* a_src = tiles + (size_t)s * TcSmem<BN, STAGES>::kStageBytes;
+                const unsigned char* b_src = a_src + TcSmem<BN, STAGES>::kABytes;
+                const uint64_t adesc = umma_desc_k_major_sw128(a_src);
+                const uint64_t bdesc = umma_desc_k_major_sw128(b_src);
+#pragma unroll
+                for (int k = 0; k < kTcBK / 16; ++k) {
+                    // 16 elements of K = 32 bytes further inside the swizzle atom: +2 in 16-byte units
+                    umma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);        // frees the stage when these MMAs have read it
+            }
+            umma_commit(acc_ready);            // arrives when every MMA issued so far has finished
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) .. +31 ----
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        bool ok = mbar_wait(acc_ready, 0);
+        if (!ok && lane == 0) { atomicExch(error_flag, 3); s_abort = 1; }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
+        tcgen05_fence_after();
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                tmem_ld_wait();
+                if (row < M) {
+                    const int n = n0 + c0;
+                    if (F32OUT) {
+                        float* dst = reinterpret_cast<float*>(out) + (size_t)row * ldo + n;
+                        if (n + 32 <= N && (ldo % 4) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                                  __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        } else {
+                            for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __uint_as_float(v[j]);
+                        }
+                    } else {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldo + n;
+                        if (n + 32 <= N && (ldo % 8) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 pk;
+                                __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                                __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                                __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                                pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
+                                pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
+                                *reinterpret_cast<uint4*>(dst + j) = pk;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown: everything issued has been waited for on the normal path; free the tensor memory ----
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D bfloat16 tensor [rows, K] with row stride ld elements; box = 64 (K) x box_rows, 128-byte swizzle, zero fill.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    CIB_REQUIRE(fn != nullptr, "gemm_tcgen05: the driver does not give cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CIB_REQUIRE(r == CUDA_SUCCESS, "gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d (rows=%d K=%d ld=%d)", (int)r, rows, K, ld);
+    return 0;
+}
+
+template <int BN, int STAGES, bool F32OUT>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int ldo, int M, int N, int K, int* error_flag,
+                     cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, F32OUT>;
+    constexpr int smem = TcSmem<BN, STAGES>::kTotal;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) {
+            set_error("gemm_tcgen05: cannot raise shared memory to %d: %s", smem, cudaGetErrorString(e));
+            return -2;
+        }
+        configured = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + kTcBM - 1) / kTcBM);
+    kernel<<<grid, 192, smem, stream>>>(ma, mw, out, ldo, M, N, K, error_flag);
+    CIB_LAUNCH_CHECK("gemm_tcgen05");
+    return 0;
+}
+
+}  // namespace cib
+
+using namespace cib;
+
+extern "C" int cib_gemm_tcgen05_supports(int M, int N, int K) {
+    return M >= 1 && N >= 8 && K >= 8 && K % 8 == 0;
+}
+
+// a: [M, K] bfloat16 rows (lda), w: [N, K] bfloat16 rows (ldw), out: [M, N] bfloat16 (out_f32 = 0) or float32.
+// error_flag: one int in device memory, zero before the call; non-zero afterwards means a bounded wait gave up.
+extern "C" int cib_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ldo, int out_f32, int M,
+                                int N, int K, int* error_flag, cudaStream_t stream) {
+    CIB_REQUIRE(cib_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M=%d N=%d K=%d is not taken (K must be a multiple of 8)", M, N, K);
+    CIB_REQUIRE(lda >= K && ldw >= K && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: row strides must be multiples of 8 elements");
+    CIB_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
+    CIB_REQUIRE(ldo >= N && error_flag != nullptr, "gemm_tcgen05: bad output arguments");
+    CUtensorMap ma, mw;
+    const bool wide = (N % 256 == 0) && ((N / 256) * ((M + 127) / 128) >= 120);
+    if (make_map(&ma, a, M, K, lda, kTcBM) != 0) return -1;
+    if (make_map(&mw, w, N, K, ldw, wide ? 256 : 128) != 0) return -1;
+    if (wide) {
+        if (out_f32) return launch_tc<256, 4, true>(ma, mw, out, ldo, M, N, K, error_flag, stream);
+        return launch_tc<256, 4, false>(ma, mw, out, ldo, M, N, K, error_flag, stream);
+    }
+    if (out_f32) return launch_tc<128, 6, true>(ma, mw, out, ldo, M, N, K, error_flag, stream);
+    return launch_tc<128, 6, false>(ma, mw, out, ldo, M, N, K, error_flag, stream);
+}

@@ -73,6 +73,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P],
         "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P],
+        "cib_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
         "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
     }
@@ -82,6 +83,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn.restype = _I
     lib.cib_paged_attention_decode_supports.argtypes = [_I, _I, _I]
     lib.cib_paged_attention_decode_supports.restype = _I
+    lib.cib_gemm_tcgen05_supports.argtypes = [_I, _I, _I]
+    lib.cib_gemm_tcgen05_supports.restype = _I
     lib.cib_gemm_skinny_supports.argtypes = [_I, _I, _I, _I]
     lib.cib_gemm_skinny_supports.restype = _I
     lib.cib_paged_attention_prefill_supports.argtypes = [_I, _I, _I]
@@ -408,6 +411,49 @@ def gemm_skinny(w: torch.Tensor, out: torch.Tensor, *, act: torch.Tensor | None 
         _cuda(residual_out, "residual_out") if residual_out is not None else None,
         _cuda(out, "out", contiguous=False), out.stride(0), M, epi, N // 2 if silu_pair else 0, 1 if use_pdl else 0, _stream())
     _check(rc, "gemm_skinny")
+    _count()
+
+
+_error_flags: dict = {}
+
+
+def _error_flag(device: torch.device) -> torch.Tensor:
+    """One int per device that kernels with bounded waits raise instead of hanging."""
+    flag = _error_flags.get(device.index)
+    if flag is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the device error flag must exist before a graph capture (run the step once eagerly first)")
+        flag = torch.zeros(1, dtype=torch.int32, device=device)
+        _error_flags[device.index] = flag
+    return flag
+
+
+def check_error_flags() -> None:
+    """Raise if a kernel gave up on a bounded wait since the last check (reads one int per device: synchronises)."""
+    for index, flag in _error_flags.items():
+        code = int(flag.item())
+        if code:
+            flag.zero_()
+            raise KernelError(f"a kernel on cuda:{index} gave up waiting on a barrier (code {code}); its results are invalid")
+
+
+def gemm_tcgen05_supports(M: int, N: int, K: int) -> bool:
+    return bool(library().cib_gemm_tcgen05_supports(M, N, K))
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T on tcgen05 tensor cores (bfloat16 in, bfloat16 or float32 out)."""
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2 or out.shape != (M, N) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tcgen05: a {list(a.shape)} {a.dtype}, w {list(w.shape)} {w.dtype}, out {list(out.shape)} do not fit")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tcgen05: rows must be dense and out bfloat16 or float32")
+    rc = library().cib_gemm_tcgen05(
+        _cuda(a, "a", contiguous=False), a.stride(0), _cuda(w, "w", contiguous=False), w.stride(0),
+        _cuda(out, "out", contiguous=False), out.stride(0), 1 if out.dtype == torch.float32 else 0, M, N, K,
+        _error_flag(a.device).data_ptr(), _stream())
+    _check(rc, "gemm_tcgen05")
     _count()
 
 

@@ -116,6 +116,27 @@ def test_gemm_generic(M, N, K, dtypes):
     assert torch.equal(one[0].cpu(), out[M // 2].cpu())
 
 
+@pytest.mark.parametrize("M, N, K", [(128, 128, 64), (128, 256, 128), (17, 1000, 96), (300, 517 + 3, 72),
+                                     (2048, 4096, 1024), (640, 1024, 3072), (129, 6144, 1024), (200, 136, 2048)])
+@pytest.mark.parametrize("f32_out", [False, True])
+def test_gemm_tcgen05(M, N, K, f32_out):
+    k = _k()
+    assert k.gemm_tcgen05_supports(M, N, K)
+    a, w = rand(M, K, seed=21, dtype=torch.bfloat16), rand(N, K, seed=22, scale=0.05, dtype=torch.bfloat16)
+    out = torch.full((M, N), 7.0, dtype=torch.float32 if f32_out else torch.bfloat16, device=DEV)
+    k.gemm_tcgen05(a.to(DEV), w.to(DEV), out)
+    k.check_error_flags()
+    want = a.to(DEV).double() @ w.to(DEV).double().T
+    close(out, want, 2e-5 if f32_out else 6e-3)
+    # rows strided inside a wider buffer (a packed row), and a second call on the same stream
+    wide = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = a.to(DEV)
+    out2 = torch.empty_like(out)
+    k.gemm_tcgen05(wide[:, :K], w.to(DEV), out2)
+    k.check_error_flags()
+    assert torch.equal(out2.cpu(), out.cpu())
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N, K", [(1024, 1024), (48, 96), (1000, 2048), (3000, 72), (151936, 1024)])
 def test_gemm_skinny(M, N, K):
