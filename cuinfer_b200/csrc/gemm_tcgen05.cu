@@ -1,7 +1,8 @@
 // out[M, N] = a[M, K] · w[N, K]^T in bfloat16 on the 5th-generation tensor cores: TMA-fed, TMEM-accumulated.
 //
 // The reference calls cuBLAS for every projection (csrc/ops/projection.cu:32-44).  This is the prompt-sized
-// replacement (many rows): one 128 x BN output tile per CTA, K walked in 64-element steps.
+// replacement (many rows).  The kernel is persistent: one CTA per SM walks over 128 x BN output tiles, K in
+// 64-element steps, and two accumulators in tensor memory let the epilogue of one tile run under the MMAs of the next.
 //
 //   warp 0, one thread : TMA producer.  Per step two `cp.async.bulk.tensor.2d` loads (an activation tile 128 x 64 and
 //                        a weight tile BN x 64, both K-major, 128-byte swizzle) into a ring of shared-memory stages,
@@ -102,36 +103,53 @@ struct TcSmem {
     static constexpr int kABytes = kTcBM * kTcBK * 2;
     static constexpr int kBBytes = BN * kTcBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kTotal = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int kStagingBytes = kTcBM * 128 * 2;        // 128 rows x 128 bfloat16 columns for the TMA store
+    static constexpr int kTotal = STAGES * kStageBytes + kStagingBytes + 1024 /* alignment slack */ + 512 /* barriers */;
 };
 
-template <int BN, int STAGES, bool F32OUT>
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(tc_smem_u32(smem_src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// TMA_STORE: bfloat16 results leave through a 128-byte-swizzled staging buffer and `cp.async.bulk.tensor` stores
+// (whole 128-byte lines per row; tails clipped by the tensor map).  Otherwise every thread stores its row itself.
+template <int BN, int STAGES, bool F32OUT, bool TMA_STORE>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    void* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ error_flag) {
+                    const __grid_constant__ CUtensorMap map_out, void* __restrict__ out, int ldo, int M, int N, int K,
+                    int* __restrict__ error_flag) {
     extern __shared__ unsigned char smem_raw[];
     // stages must start on a 1024-byte boundary (one swizzle atom)
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * TcSmem<BN, STAGES>::kStageBytes);
-    uint64_t* full = bars;                 // [STAGES]
-    uint64_t* empty = bars + STAGES;       // [STAGES]
-    uint64_t* acc_ready = bars + 2 * STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    unsigned char* staging = tiles + STAGES * TcSmem<BN, STAGES>::kStageBytes;      // 1024-byte aligned as well
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + TcSmem<BN, STAGES>::kStagingBytes);
+    uint64_t* full = bars;                     // [STAGES]  bytes of a stage have landed
+    uint64_t* empty = bars + STAGES;           // [STAGES]  the MMAs that read a stage are done
+    uint64_t* acc_full = bars + 2 * STAGES;    // [2]       an accumulator holds a finished tile
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]    the epilogue has read an accumulator
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     __shared__ int s_abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * kTcBM, n0 = blockIdx.x * BN;
     const int k_steps = (K + kTcBK - 1) / kTcBK;
+    const int n_blocks = (N + BN - 1) / BN, m_blocks = (M + kTcBM - 1) / kTcBM;
+    const int num_tiles = n_blocks * m_blocks;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tcgen05_fence_before();
@@ -141,56 +159,124 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- TMA producer ----
-            for (int kb = 0; kb < k_steps; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t phase = (kb / STAGES) & 1;
-                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 1); s_abort = 1; break; }
-                if (*(volatile int*)&s_abort) break;
-                unsigned char* a_dst = tiles + (size_t)s * TcSmem<BN, STAGES>::kStageBytes;
-                unsigned char* b_dst = a_dst + TcSmem<BN, STAGES>::kABytes;
-                mbar_expect_tx(&full[s], TcSmem<BN, STAGES>::kStageBytes);
-                tma_load_2d(a_dst, &map_a, &full[s], kb * kTcBK, m0);
-                tma_load_2d(b_dst, &map_w, &full[s], kb * kTcBK, n0);
+            // ---- TMA producer: one running step counter over all tiles of this CTA ----
+            int step = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / n_blocks) * kTcBM, n0 = (tile % n_blocks) * BN;
+                for (int kb = 0; kb < k_steps; ++kb, ++step) {
+                    const int s = step % STAGES;
+                    const uint32_t phase = (step / STAGES) & 1;
+                    if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 1); s_abort = 1; ok = false; break; }
+                    if (*(volatile int*)&s_abort) { ok = false; break; }
+                    unsigned char* a_dst = tiles + (size_t)s * TcSmem<BN, STAGES>::kStageBytes;
+                    unsigned char* b_dst = a_dst + TcSmem<BN, STAGES>::kABytes;
+                    mbar_expect_tx(&full[s], TcSmem<BN, STAGES>::kStageBytes);
+                    tma_load_2d(a_dst, &map_a, &full[s], kb * kTcBK, m0);
+                    tma_load_2d(b_dst, &map_w, &full[s], kb * kTcBK, n0);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer ----
             constexpr uint32_t idesc = umma_idesc_bf16(kTcBM, BN);
+            int step = 0, local = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_steps && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t phase = (kb / STAGES) & 1;
-                if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 2); s_abort = 1; ok = false; break; }
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1)) { atomicExch(error_flag, 4); s_abort = 1; ok = false; break; }
                 tcgen05_fence_after();
-                const unsigned char* a_src = tiles + (size_t)s * TcSmem<BN, STAGES>::kStageBytes;
-                const unsigned char* b_src = a_src + TcSmem<BN, STAGES>::kABytes;
-                const uint64_t adesc = umma_desc_k_major_sw128(a_src);
-                const uint64_t bdesc = umma_desc_k_major_sw128(b_src);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < k_steps; ++kb, ++step) {
+                    const int s = step % STAGES;
+                    const uint32_t phase = (step / STAGES) & 1;
+                    if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 2); s_abort = 1; ok = false; break; }
+                    tcgen05_fence_after();
+                    const unsigned char* a_src = tiles + (size_t)s * TcSmem<BN, STAGES>::kStageBytes;
+                    const unsigned char* b_src = a_src + TcSmem<BN, STAGES>::kABytes;
+                    const uint64_t adesc = umma_desc_k_major_sw128(a_src);
+                    const uint64_t bdesc = umma_desc_k_major_sw128(b_src);
 #pragma unroll
-                for (int k = 0; k < kTcBK / 16; ++k) {
-                    // 16 elements of K = 32 bytes further inside the swizzle atom: +2 in 16-byte units
-                    umma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < kTcBK / 16; ++k) {
+                        // 16 elements of K = 32 bytes further inside the swizzle atom: +2 in 16-byte units
+                        umma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);        // frees the stage when these MMAs have read it
                 }
-                umma_commit(&empty[s]);        // frees the stage when these MMAs have read it
+                umma_commit(&acc_full[buf]);       // arrives when every MMA issued so far has finished
             }
-            umma_commit(acc_ready);            // arrives when every MMA issued so far has finished
         }
     } else {
         // ---- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) .. +31 ----
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        bool ok = mbar_wait(acc_ready, 0);
-        if (!ok && lane == 0) { atomicExch(error_flag, 3); s_abort = 1; }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
-        tcgen05_fence_after();
-        if (ok) {
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            const int m0 = (tile / n_blocks) * kTcBM, n0 = (tile % n_blocks) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            ok = mbar_wait(&acc_full[buf], acc_phase);
+            if (!ok && lane == 0) { atomicExch(error_flag, 3); s_abort = 1; }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
+            if (!ok) break;
+            tcgen05_fence_after();
+            if (TMA_STORE) {
+                const int r_local = quarter * 32 + lane;                 // row of the tile = TMEM lane
+                const bool store_thread = threadIdx.x == 64;
+#pragma unroll 1
+                for (int half = 0; half < BN / 128; ++half) {
+                    if (store_thread) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging is free again
+                    epilogue_barrier();
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128 + c * 32), v);
+                        tmem_ld_wait();
+                        if (half == BN / 128 - 1 && c == 3) {
+                            tcgen05_fence_before();
+                            if (lane == 0) mbar_arrive(&acc_empty[buf]);     // the accumulator has been read completely
+                        }
+                        // 32 columns = 64 bytes = four 16-byte chunks of this row, in panel c / 2, chunks (c % 2) * 4 ..
+                        unsigned char* panel = staging + (size_t)(c >> 1) * (kTcBM * 128) + (size_t)r_local * 128;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 pk;
+                            __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]));
+                            __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                            __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                            pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
+                            const int chunk = ((c & 1) * 4 + j) ^ (r_local & 7);       // 128-byte swizzle
+                            *reinterpret_cast<uint4*>(panel + chunk * 16) = pk;
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    epilogue_barrier();
+                    if (store_thread) {
+#pragma unroll
+                        for (int p = 0; p < 2; ++p) {
+                            const int col = n0 + half * 128 + p * 64;
+                            if (col < N) tma_store_2d(&map_out, staging + (size_t)p * (kTcBM * 128), col, m0);
+                        }
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
                 tmem_ld_wait();
+                if (c0 + 32 >= BN) {
+                    // the accumulator has been read completely: hand it back before the stores
+                    tcgen05_fence_before();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                }
                 if (row < M) {
                     const int n = n0 + c0;
                     if (F32OUT) {
@@ -201,7 +287,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
                                                                                   __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
                         } else {
-                            for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __uint_as_float(v[j]);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n + j < N) dst[j] = __uint_as_float(v[j]);
                         }
                     } else {
                         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldo + n;
@@ -218,7 +306,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 *reinterpret_cast<uint4*>(dst + j) = pk;
                             }
                         } else {
-                            for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
                         }
                     }
                 }
@@ -226,10 +316,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     }
     // ---- teardown: everything issued has been waited for on the normal path; free the tensor memory ----
+    if (TMA_STORE && threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
     }
 }
 
@@ -263,10 +354,10 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
     return 0;
 }
 
-template <int BN, int STAGES, bool F32OUT>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int ldo, int M, int N, int K, int* error_flag,
-                     cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_kernel<BN, STAGES, F32OUT>;
+template <int BN, int STAGES, bool F32OUT, bool TMA_STORE>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, void* out, int ldo, int M, int N,
+                     int K, int* error_flag, cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, F32OUT, TMA_STORE>;
     constexpr int smem = TcSmem<BN, STAGES>::kTotal;
     static bool configured = false;
     if (!configured) {
@@ -277,8 +368,15 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, in
         }
         configured = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + kTcBM - 1) / kTcBM);
-    kernel<<<grid, 192, smem, stream>>>(ma, mw, out, ldo, M, N, K, error_flag);
+    static int num_sms = 0;
+    if (num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
+    }
+    const int tiles = ((N + BN - 1) / BN) * ((M + kTcBM - 1) / kTcBM);
+    dim3 grid(tiles < num_sms ? tiles : num_sms);
+    kernel<<<grid, 192, smem, stream>>>(ma, mw, mo, out, ldo, M, N, K, error_flag);
     CIB_LAUNCH_CHECK("gemm_tcgen05");
     return 0;
 }
@@ -300,13 +398,22 @@ extern "C" int cib_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, 
     CIB_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
     CIB_REQUIRE(ldo >= N && error_flag != nullptr, "gemm_tcgen05: bad output arguments");
     CUtensorMap ma, mw;
-    const bool wide = (N % 256 == 0) && ((N / 256) * ((M + 127) / 128) >= 120);
+    // Tile width: 256 when that still gives most SMs a tile, else 128.
+    const int m_blocks = (M + 127) / 128;
+    int bn = 128;
+    if (N % 256 == 0 && (N / 256) * m_blocks >= 120) bn = 256;
     if (make_map(&ma, a, M, K, lda, kTcBM) != 0) return -1;
-    if (make_map(&mw, w, N, K, ldw, wide ? 256 : 128) != 0) return -1;
-    if (wide) {
-        if (out_f32) return launch_tc<256, 4, true>(ma, mw, out, ldo, M, N, K, error_flag, stream);
-        return launch_tc<256, 4, false>(ma, mw, out, ldo, M, N, K, error_flag, stream);
+    if (make_map(&mw, w, N, K, ldw, bn) != 0) return -1;
+    // bfloat16 results with 16-byte aligned rows leave by TMA store; anything else is stored by the threads
+    const bool tma_out = !out_f32 && ldo % 8 == 0 && ((uintptr_t)out % 16) == 0;
+    CUtensorMap mo = ma;
+    if (tma_out && make_map(&mo, out, M, N, ldo, kTcBM) != 0) return -1;
+    if (bn == 256) {
+        if (out_f32) return launch_tc<256, 4, true, false>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream);
+        if (tma_out) return launch_tc<256, 4, false, true>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream);
+        return launch_tc<256, 4, false, false>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream);
     }
-    if (out_f32) return launch_tc<128, 6, true>(ma, mw, out, ldo, M, N, K, error_flag, stream);
-    return launch_tc<128, 6, false>(ma, mw, out, ldo, M, N, K, error_flag, stream);
+    if (out_f32) return launch_tc<128, 5, true, false>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream);
+    if (tma_out) return launch_tc<128, 5, false, true>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream);
+    return launch_tc<128, 5, false, false>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream);
 }

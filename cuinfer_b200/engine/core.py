@@ -11,6 +11,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
+from .. import kernels
 from ..config import EngineConfig
 from ..sampling import Sampler, SamplingParams
 from .runner import ModelRunner, StepEntry
@@ -79,4 +80,5 @@ class EngineCore:
             [s.request.num_output_tokens for s in wanted])
         self.runner.mark_device_end()
         host = ids.cpu().tolist()
+        kernels.check_error_flags()
         return [(s.request.request_id, tok) for s, tok in zip(wanted, host)]

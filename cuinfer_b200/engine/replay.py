@@ -20,6 +20,7 @@ import os
 import sys
 from typing import List, Optional
 
+from .. import kernels
 from ..config import EngineConfig
 from .runner import ModelRunner, StepEntry
 
@@ -62,6 +63,7 @@ def run_trace(runner: ModelRunner, lines, out_dir: str, log=sys.stdout) -> int:
             logits = runner.step(entries)
             if logits.shape[0]:
                 host = logits.float().cpu().contiguous().numpy().astype("<f4", copy=False)
+                kernels.check_error_flags()
                 with open(os.path.join(out_dir, f"{step_id}.f32"), "wb") as fh:
                     fh.write(host.tobytes())
         for rid in ended:

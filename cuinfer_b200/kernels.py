@@ -428,8 +428,16 @@ def _error_flag(device: torch.device) -> torch.Tensor:
     return flag
 
 
+_flagged_launches = 0
+
+
 def check_error_flags() -> None:
-    """Raise if a kernel gave up on a bounded wait since the last check (reads one int per device: synchronises)."""
+    """Raise if a kernel gave up on a bounded wait since the last check.  Reads one int per device (which
+    synchronises), but only if such a kernel was launched since the last check."""
+    global _flagged_launches
+    if _flagged_launches == 0:
+        return
+    _flagged_launches = 0
     for index, flag in _error_flags.items():
         code = int(flag.item())
         if code:
@@ -454,6 +462,8 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         _cuda(out, "out", contiguous=False), out.stride(0), 1 if out.dtype == torch.float32 else 0, M, N, K,
         _error_flag(a.device).data_ptr(), _stream())
     _check(rc, "gemm_tcgen05")
+    global _flagged_launches
+    _flagged_launches += 1
     _count()
 
 

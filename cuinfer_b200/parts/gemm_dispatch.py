@@ -1,14 +1,23 @@
 """Choice of the bfloat16 matrix-product kernel for a given shape.
 
-Order of preference: this package's tensor-core kernels, then the library product (cuBLAS via
-``torch.mm``; the reference calls cuBLAS for every projection, csrc/ops/projection.cu:32-44), then
-the FMA kernel for shapes cuBLAS's tensor-core paths do not take.  A shape no kernel takes raises.
+* up to 16 rows (decode steps): the few-rows kernel (``gemm_skinny``), weights streamed once;
+* 128 rows and more (prompt portions): the tcgen05 / TMA / TMEM kernel (``gemm_tcgen05``);
+* in between, and for K that is not a multiple of 8: the library product (cuBLAS via ``torch.mm``; the reference
+  calls cuBLAS for every projection, csrc/ops/projection.cu:32-44), or the FMA kernel for shapes cuBLAS's
+  tensor-core paths do not take.
+
+``CUINFER_B200_GEMM=cublas`` sends every prompt-sized product to the library (for comparisons).
 """
 from __future__ import annotations
 
 import torch
 
+import os
+
 from .. import kernels
+
+TCGEN05_MIN_ROWS = 128
+_FORCE_CUBLAS = os.environ.get("CUINFER_B200_GEMM", "") == "cublas"
 
 
 def bf16_matmul_nt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -17,6 +26,10 @@ def bf16_matmul_nt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     N = weight.shape[0]
     if M <= 16 and weight.is_contiguous() and kernels.gemm_skinny_supports(M, N, K):
         kernels.gemm_skinny(weight, out, act=x)
+        return
+    if (M >= TCGEN05_MIN_ROWS and not _FORCE_CUBLAS and x.stride(1) == 1 and weight.stride(1) == 1
+            and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and kernels.gemm_tcgen05_supports(M, N, K)):
+        kernels.gemm_tcgen05(x, weight, out)
         return
     if K % 8 == 0 and N % 8 == 0 and x.is_contiguous() and weight.is_contiguous():
         if out.dtype == torch.bfloat16:
