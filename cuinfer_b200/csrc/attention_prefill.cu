@@ -47,14 +47,14 @@ __device__ __forceinline__ void pf_load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16
 }
 
 template <int D>
-__global__ void __launch_bounds__(kPfWarps * 32)
+__global__ void __launch_bounds__(kPfWarps * 32, 3)
 paged_attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                                int out_stride, const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
                                const int* __restrict__ block_table, int table_stride,
                                const int* __restrict__ query_start_loc, const int* __restrict__ seq_lens,
-                               int num_requests, int nq, int nkv, float scale_log2, int window) {
+                               int num_requests, int nq, int nkv, float scale_log2, int window, int pair) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ int s_req, s_tile;
+    __shared__ int s_req, s_tile, s_ntiles;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = lane & 3, qrow = lane >> 2;
     const int kvh = blockIdx.y;
@@ -62,28 +62,37 @@ paged_attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
 
     // ---- which request and which of its row tiles is this CTA? ----
     if (tid == 0) {
-        // later tiles of a request see more keys: hand them out first so that the long ones do not end the launch
-        int t = gridDim.x - 1 - blockIdx.x, r = 0;
+        // A CTA takes a pair of row tiles of one request: tile p and tile (tiles - 1 - p).  Under the causal mask
+        // tile i sees about i + 1 key tiles, so every pair carries the same work and the launch ends evenly.
+        int t = blockIdx.x, r = 0, tiles = 0;
         for (; r < num_requests; ++r) {
-            const int tiles = ((query_start_loc[r + 1] - query_start_loc[r]) * g + kPfM - 1) / kPfM;
-            if (t < tiles) break;
-            t -= tiles;
+            tiles = ((query_start_loc[r + 1] - query_start_loc[r]) * g + kPfM - 1) / kPfM;
+            const int pairs = pair ? (tiles + 1) / 2 : tiles;
+            if (t < pairs) break;
+            t -= pairs;
         }
         s_req = r;
         s_tile = t;
+        s_ntiles = tiles;
     }
     __syncthreads();
     const int r = s_req;
     if (r >= num_requests) return;
+    const int pair_first = s_tile, pair_second = pair ? s_ntiles - 1 - s_tile : s_tile;
+    for (int which = 0; which < 2; ++which) {
+    if (which == 1 && pair_second == pair_first) break;
+    const int tile_index = which == 0 ? pair_second : pair_first;      // the longer one first
+    __syncthreads();                                                    // shared memory of the first tile is free
     const int q0 = query_start_loc[r];
     const int n = query_start_loc[r + 1] - q0;
     const int seq_len = seq_lens[r];
     const int rows_total = n * g;
-    const int row0 = s_tile * kPfM;
+    const int row0 = tile_index * kPfM;
     const int* table = block_table + (size_t)r * table_stride;
 
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [64][D]
-    __nv_bfloat16* sKV = sQ + kPfM * D;                                              // stages x (K [64][D], V [64][D])
+    // two stages of (K [64][D], V [64][D]); the query tile borrows stage 1 until its fragments are in registers
+    __nv_bfloat16* sKV = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* sQ = sKV + (size_t)2 * kPfN * D;
     auto stage_k = [&](int s) { return sKV + (size_t)s * 2 * kPfN * D; };
     auto stage_v = [&](int s) { return sKV + (size_t)s * 2 * kPfN * D + kPfN * D; };
 
@@ -125,6 +134,7 @@ paged_attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
             ldmatrix_x4(qf[kt], smem_u32(sQ + row * D + ((chunk ^ (row & 7)) * 8)));
         }
     }
+    __syncthreads();          // every warp has its query fragments: stage 1 may now take keys and values
     // positions of this lane's two rows
     int pos_row[2];
     bool row_ok[2];
@@ -253,14 +263,15 @@ paged_attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
             *reinterpret_cast<uint32_t*>(dst + nt * 8 + quad * 2) = pack_bf16(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
         }
     }
+    }   // the pair's second tile
 }
 
 template <int D>
 static int launch_prefill(const void* q, int q_stride, void* out, int out_stride, const void* cache, int num_pages,
                           int page_size, const int* block_table, int table_stride, const int* query_start_loc,
                           const int* seq_lens, int num_requests, int num_tiles, int nq, int nkv, float scale, int window,
-                          cudaStream_t stream) {
-    const size_t smem = (size_t)(kPfM * D + kPfStages * 2 * kPfN * D) * sizeof(__nv_bfloat16);
+                          int pair, cudaStream_t stream) {
+    const size_t smem = (size_t)(kPfStages * 2 * kPfN * D) * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -274,7 +285,7 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
     paged_attention_prefill_kernel<D><<<grid, kPfWarps * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache, num_pages,
         page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, nq, nkv,
-        scale * 1.4426950408889634f, window);
+        scale * 1.4426950408889634f, window, pair);
     CIB_LAUNCH_CHECK("paged_attention_prefill");
     return 0;
 }
@@ -287,12 +298,14 @@ extern "C" int cib_paged_attention_prefill_supports(int head_dim, int nq, int nk
     return (head_dim == 64 || head_dim == 128) && nkv > 0 && nq % nkv == 0;
 }
 
-// num_tiles = sum over requests of ceil(tokens_r * (nq / nkv) / 64), computed by the caller.
+// num_tiles = number of CTAs along x: with pair = 0 the sum over requests of t_r = ceil(tokens_r * (nq / nkv) / 64);
+// with pair = 1 a CTA takes the row tiles p and t_r - 1 - p of a request (equal work under the causal mask) and
+// num_tiles is the sum of ceil(t_r / 2).
 extern "C" int cib_paged_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* cache,
                                            int num_pages, int page_size, const int* block_table, int table_stride,
                                            const int* query_start_loc, const int* seq_lens, int num_requests,
                                            int num_tiles, int nq, int nkv, int head_dim, float scale, int window,
-                                           cudaStream_t stream) {
+                                           int pair, cudaStream_t stream) {
     CIB_REQUIRE(cib_paged_attention_prefill_supports(head_dim, nq, nkv),
                 "paged_attention_prefill: head_dim %d is not taken by this kernel (64 or 128)", head_dim);
     CIB_REQUIRE(num_requests >= 0 && num_tiles >= 0 && nkv <= 65535, "paged_attention_prefill: bad sizes");
@@ -301,6 +314,6 @@ extern "C" int cib_paged_attention_prefill(const void* q, int q_stride, void* ou
                 "paged_attention_prefill: q rows must be 16-byte aligned and out rows 4-byte aligned");
     if (num_requests == 0 || num_tiles == 0) return 0;
     if (head_dim == 64)
-        return launch_prefill<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, num_tiles, nq, nkv, scale, window, stream);
-    return launch_prefill<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, num_tiles, nq, nkv, scale, window, stream);
+        return launch_prefill<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, num_tiles, nq, nkv, scale, window, pair, stream);
+    return launch_prefill<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, num_tiles, nq, nkv, scale, window, pair, stream);
 }

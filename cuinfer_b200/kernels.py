@@ -71,7 +71,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_qk_norm_rope_kv_write": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
         "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P],
-        "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+        "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
         "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P],
         "cib_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
@@ -322,13 +322,17 @@ def paged_attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Ten
     if q.stride(1) != 1 or out.stride(1) != 1 or out.shape != (T, num_q_heads * head_dim):
         raise KernelError("paged_attention_prefill: q/out rows must be dense and out [T, nq*d]")
     g = num_q_heads // num_kv_heads
-    tiles = sum((n * g + 63) // 64 for n in query_lens_host)
+    # CTAs take 64-row tiles one by one, or in pairs (tile p with tile t-1-p: equal work under the causal mask)
+    # when the pairs alone still fill the GPU
+    paired = sum(((n * g + 63) // 64 + 1) // 2 for n in query_lens_host)
+    pair = 1 if paired * num_kv_heads >= 200 else 0
+    tiles = paired if pair else sum((n * g + 63) // 64 for n in query_lens_host)
     rc = library().cib_paged_attention_prefill(
         _cuda(q, "q", contiguous=False), q.stride(0), _cuda(out, "out", contiguous=False), out.stride(0),
         _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
         block_table.stride(0), _cuda(query_start_loc, "query_start_loc", torch.int32),
         _cuda(seq_lens, "seq_lens", torch.int32), len(query_lens_host), tiles, num_q_heads, num_kv_heads, head_dim,
-        float(scale), int(window), _stream())
+        float(scale), int(window), pair, _stream())
     _check(rc, "paged_attention_prefill")
     _count()
 
