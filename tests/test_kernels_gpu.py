@@ -372,6 +372,46 @@ def test_paged_attention_prefill(nq, nkv, d, ps, window):
     close(out, attention_reference(case, lens, new, scale, window), 1.5e-2)
 
 
+@pytest.mark.parametrize("nq, nkv, d, ps, rot, norm", [(16, 8, 128, 16, 128, True), (8, 2, 64, 32, 32, True),
+                                                          (12, 3, 128, 5, 0, False), (4, 4, 64, 16, 64, False)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_paged_attention_decode_fused_equals_the_two_kernels(nq, nkv, d, ps, rot, norm, splits):
+    """The attention kernel with norm, encoding and cache write folded in gives what the separate kernel before it
+    plus the plain attention kernel give, and leaves the same cache behind."""
+    k = _k()
+    lens = [1, 2, 16, 17, 64, 333, 1000]
+    R = len(lens)
+    case = attention_case(torch.bfloat16, nq, nkv, d, lens, [1] * R, ps, seed=70)
+    cache0, bt = case["cache"].to(DEV), case["bt"].to(DEV)
+    qkv = rand(R, (nq + 2 * nkv) * d, seed=71, dtype=torch.bfloat16).to(DEV)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(bt[r, (n - 1) // ps]) * ps + (n - 1) % ps for r, n in enumerate(lens)], dtype=torch.int32, device=DEV)
+    slots[2] = -1                                     # a padding row writes nothing
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    qw = (1 + rand(d, seed=72, scale=0.3)).to(torch.bfloat16).to(DEV) if norm else None
+    kw = (1 + rand(d, seed=73, scale=0.3)).to(torch.bfloat16).to(DEV) if norm else None
+    table = None
+    if rot:
+        inv = 1.0 / torch.pow(torch.tensor(10000.0), torch.arange(rot // 2, dtype=torch.float32) * 2.0 / rot)
+        ang = torch.arange(1100, dtype=torch.float32)[:, None] * inv[None, :]
+        table = torch.stack((torch.cos(ang), torch.sin(ang)), -1).contiguous().to(DEV)
+    scale = 1.0 / math.sqrt(d)
+    # the two kernels
+    cache_a, rows_a = cache0.clone(), qkv.clone()
+    k.qk_norm_rope_kv_write(rows_a, positions, slots, qw, kw, 1e-5, table, rot, cache_a, nq, nkv, d)
+    want = torch.empty(R, nq * d, dtype=torch.bfloat16, device=DEV)
+    k.paged_attention_decode(rows_a, want, cache_a, bt, sl, nq, nkv, d, scale, 0, splits)
+    # the fused kernel
+    cache_b = cache0.clone()
+    got = torch.full_like(want, 5.0)
+    for _ in range(2):
+        k.paged_attention_decode_fused(qkv, got, cache_b, bt, sl, positions, slots, qw, kw, 1e-5, table, rot, nq, nkv, d,
+                                       scale, 0, splits)
+    rows = [r for r in range(R) if r != 2]            # row 2 has no slot: the two-kernel path reads a stale key there
+    assert torch.equal(got[rows].cpu(), want[rows].cpu())
+    assert torch.equal(cache_b.cpu(), cache_a.cpu())
+
+
 def test_paged_attention_decode_refuses_other_sizes():
     k = _k()
     assert not k.paged_attention_decode_supports(48, 6, 3)
