@@ -172,8 +172,9 @@ def measure_decode(folder: str, batch: int, steps: int, warmup: int, args, sampl
         "tokens_per_s": tokens / (device_ms / 1e3), "ms_per_step": device_ms / steps,
         "e2e_tokens_per_s": tokens / wall, "e2e_ms_per_step": wall * 1e3 / steps, "launches": launches,
         "graph_steps": graph_steps, "context_mid": ctx_mid, "prompt_len": prompt_len, "clocks": clock_info,
-        "h2d_bytes": (engine.runner._graphs[next(iter(engine.runner._graphs))].total * 4 if engine.runner._graphs else 0)
-        + batch * 16,
+        # the step's arena (token ids, positions, slot mapping, lengths, block-table rows) from pinned memory;
+        # greedy sampling options stay on the device from step to step
+        "h2d_bytes": (engine.runner._graphs[next(iter(engine.runner._graphs))].total * 4 if engine.runner._graphs else 0),
         "d2h_bytes": batch * 4,
     }
     while engine.has_requests():

@@ -194,6 +194,22 @@ class ModelRunner:
         if total > self.config.max_num_scheduled_tokens:
             raise StepError(f"{total} tokens in one step exceed max_num_scheduled_tokens={self.config.max_num_scheduled_tokens}")
 
+    def _validate_decode(self, entries: Sequence[StepEntry]) -> None:
+        """The checks of ``_validate`` for a step in which every request brings one token."""
+        if not entries or len(entries) > self.config.max_num_seqs:
+            self._validate(entries)
+        mgr = self.manager
+        seen = set()
+        for e in entries:
+            rid = e.request_id
+            tok = e.tokens[0]
+            if (len(e.tokens) != 1 or rid in seen or rid not in mgr or not 0 <= tok < self.vocab_size
+                    or mgr.num_tokens(rid) + 1 > self.max_model_len or any(p > 0 for p in mgr.pages_needed(rid, 1))
+                    or any(w != 0 for w in e.want)):
+                self._validate(entries)          # raises with the full message
+                raise StepError(f"request {rid!r} cannot take part in a decode step")
+            seen.add(rid)
+
     def build_context(self, entries: Sequence[StepEntry], table_stride: Optional[int] = None):
         """Pack the batch, copy it to the device and return ``(StepContext, logits_indices tensor)``."""
         mgr = self.manager
@@ -330,7 +346,7 @@ class ModelRunner:
     def decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """One decode step (every entry brings one token and wants its logits) by graph replay.
         Returns float32 logits ``[len(entries), vocab]``; the tensor is overwritten by the next decode step."""
-        self._validate(entries)
+        self._validate_decode(entries)
         self.storage.zero_slots(self.manager.take_newly_admitted())
         graph = self.decode_graph(len(entries))
         graph.upload(entries)
@@ -375,6 +391,7 @@ class DecodeGraph:
         self.total = off
         self.pinned = [torch.empty(off, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.events: List[Optional[torch.cuda.Event]] = [None, None]
+        self.row_state = [[[None] * rows for _ in range(G)] for _ in range(2)]   # per staging buffer, group, row
         self.turn = 0
         self.arena = torch.zeros(off, dtype=torch.int32, device=runner.device)
         for buf in self.pinned:
@@ -450,18 +467,31 @@ class DecodeGraph:
         sl[n:] = 1
         slots[:n] = [mgr.slot(e.request_id) for e in entries]
         slots[n:] = 0
+        # Block-table rows change rarely (a page every page_size steps): each staging buffer remembers which
+        # request and how many pages every row holds, and only new entries are written.
+        state = self.row_state[i]
         for g in range(len(r.groups)):
             sm = self._view(host, f"sm{g}")
             bt = self._view(host, f"bt{g}").reshape(B, P)
-            bt[n:, :] = -1
+            windowed = r.groups[g].window is not None
+            for row in range(n, B):
+                if state[g][row] is not None:
+                    bt[row, :] = -1
+                    state[g][row] = None
             sm[n:] = -1
             for row, (e, start) in enumerate(zip(entries, starts)):
                 table = mgr.block_table(e.request_id, g)
                 k = len(table)
                 if k > P:
                     raise StepError(f"request {e.request_id!r} holds {k} pages, more than the graph's table stride {P}")
-                bt[row, :k] = table
-                bt[row, k:] = -1
+                known = state[g][row]
+                if not windowed and known is not None and known[0] == e.request_id and known[1] <= k:
+                    if known[1] < k:
+                        bt[row, known[1]:k] = table[known[1]:k]
+                else:
+                    bt[row, :k] = table
+                    bt[row, k:] = -1
+                state[g][row] = (e.request_id, k)
                 page = table[start // ps]
                 if page < 0:
                     raise StepError(f"request {e.request_id!r}: its new token has no page in group {g}")

@@ -32,6 +32,9 @@ def uniform(seed: int, request_key: int, output_index: int) -> float:
     return (h >> 40) / float(1 << 24)
 
 
+_GREEDY = SamplingParams(temperature=0.0)
+
+
 class Sampler:
     def __init__(self, seed: int, device: torch.device, max_rows: int) -> None:
         self.seed = seed
@@ -39,6 +42,7 @@ class Sampler:
         self._host = torch.empty((max(1, max_rows), 4), dtype=torch.float32, pin_memory=True)
         self._dev = torch.empty((max(1, max_rows), 4), dtype=torch.float32, device=device)
         self._ids = torch.empty(max(1, max_rows), dtype=torch.int32, device=device)
+        self._greedy_rows = 0          # leading rows of the device buffer that hold plain argmax options
 
     def pack(self, params: Sequence[SamplingParams], request_keys: Sequence[int], output_indices: Sequence[int]) -> int:
         rows = len(params)
@@ -54,10 +58,19 @@ class Sampler:
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], request_keys: Sequence[int],
                output_indices: Sequence[int]) -> torch.Tensor:
         """Token ids (int32, on the device) drawn from float32 ``logits[rows, vocab]``."""
-        rows = self.pack(params, request_keys, output_indices)
+        rows = len(params)
         if logits.shape[0] != rows:
             raise ValueError(f"{logits.shape[0]} logits rows for {rows} requests")
-        self._dev[:rows].copy_(self._host[:rows], non_blocking=True)
+        if all(p.greedy for p in params):
+            # argmax rows need no uniform number: the packed rows on the device stay valid from step to step
+            if self._greedy_rows < rows:
+                self.pack([_GREEDY] * rows, [0] * rows, [0] * rows)
+                self._dev[:rows].copy_(self._host[:rows], non_blocking=True)
+                self._greedy_rows = rows
+        else:
+            self.pack(params, request_keys, output_indices)
+            self._dev[:rows].copy_(self._host[:rows], non_blocking=True)
+            self._greedy_rows = 0
         out = self._ids[:rows]
         kernels.sample(logits, self._dev[:rows], out)
         return out
