@@ -74,11 +74,16 @@ def attention_prefill(args) -> dict:
     scale = 1.0 / math.sqrt(d)
 
     def run(i):
-        kernels.paged_attention_prefill(q, out, cache, table, qsl, sl, [n], nq, nkv, d, scale, 0)
+        if args.impl == "tcgen05":
+            kernels.attention_tcgen05(q, out, cache, table, qsl, sl, [n], nq, nkv, d, scale, 0)
+        else:
+            kernels.paged_attention_prefill(q, out, cache, table, qsl, sl, [n], nq, nkv, d, scale, 0)
 
     ms = _time(run, args.iters)
+    if args.impl == "tcgen05":
+        kernels.check_error_flags()
     flops = 4.0 * nq * d * (n * prefix + n * (n + 1) / 2.0)
-    return {"kernel": "paged_attention_prefill", "tokens": n, "prefix": prefix, "ms": round(ms, 4),
+    return {"kernel": f"attention_prefill[{args.impl}]", "tokens": n, "prefix": prefix, "ms": round(ms, 4),
             "TFLOPs": round(flops / ms / 1e9, 1)}
 
 
@@ -130,6 +135,7 @@ def main(argv=None) -> int:
     f.add_argument("--kv-heads", type=int, default=8)
     f.add_argument("--head-dim", type=int, default=128)
     f.add_argument("--page-size", type=int, default=16)
+    f.add_argument("--impl", default="mma", choices=["mma", "tcgen05"])
     f.add_argument("--iters", type=int, default=10)
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=8)

@@ -1,0 +1,499 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores (head size 128, bfloat16).
+//
+// Same contract as csrc/ops/paged_attention.cu:133-383 of the reference (queries are the last n positions of a
+// request, keys 0..position come from its pages, rows of a tile are query token x query head of one kv head), on
+// Blackwell's own path instead of mma.sync:
+//
+//   * a CTA owns a 128-row query tile (128 / g tokens x g heads of one kv head) and walks over 128-key tiles;
+//   * keys and values are gathered page by page by four producer warps with 16-byte `cp.async` copies that write
+//     the 128-byte-swizzled layout the tensor cores read (a 16-slot page is a 2 KB box per 64 columns: as TMA boxes
+//     that small the copies were issue-bound, 32 per tile), double-buffered, handed over through mbarriers;
+//   * S = Q K^T and O += P V are `tcgen05.mma.cta_group::1.kind::f16` with accumulators in tensor memory: two S
+//     buffers (128 columns each) and O (128 columns); K is a K-major operand, V an MN-major one, straight from the
+//     page layout;
+//   * four warps do the softmax, one thread per row (TMEM lane = row): they read S with `tcgen05.ld`, keep a running
+//     maximum in base 2 that is only raised when it grows by more than 8 (so O in tensor memory is rescaled rarely,
+//     with `tcgen05.ld`/`tcgen05.st`), write P in bfloat16 to a swizzled shared-memory tile (the A operand of P V);
+//   * a fifth warp's first lane issues the MMAs; S of tile j+1 is computed while the softmax of tile j runs.
+//
+// Every mbarrier wait is bounded; on a time-out the kernel raises the error flag, stops, frees its tensor memory
+// and returns.
+#include "common.cuh"
+
+
+namespace cib {
+namespace fa {
+
+constexpr int kD = 128;          // head size
+constexpr int kM = 128;          // rows per CTA
+constexpr int kN = 128;          // keys per tile
+constexpr int kPanel = kM * 128; // bytes of one 64-column panel of a 128-row tile
+constexpr long long kWaitCycles = 400000000ll;     // about 0.2 s
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void bar_init(uint64_t* b, uint32_t n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n)); }
+__device__ __forceinline__ void bar_expect(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint64_t* b) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory"); }
+__device__ __forceinline__ bool bar_try(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait(uint64_t* b, uint32_t parity) {
+    if (bar_try(b, parity)) return true;
+    const long long t0 = clock64();
+    while (clock64() - t0 < kWaitCycles)
+        if (bar_try(b, parity)) return true;
+    return false;
+}
+// K-major operand, 128-byte swizzle: 8-row atoms 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(const void* smem) {
+    return (uint64_t)((s32(smem) & 0x3ffff) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (values: [key][d], d contiguous), 128-byte swizzle: 64-element panels `panel_bytes` apart (leading
+// offset), 8-key groups 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(const void* smem, uint32_t panel_bytes) {
+    return (uint64_t)((s32(smem) & 0x3ffff) >> 4) | ((uint64_t)(panel_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// D = F32, A = B = BF16, M = 128, N = 128; b_mn: B is MN-major.
+__host__ __device__ constexpr uint32_t idesc(bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void commit(uint64_t* b) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tst32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tst_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// shared memory: Q | K0 | K1 | V0 | V1 | P, each 128 rows x 128 columns bf16 = 32 KB as two 64-column panels
+constexpr int kTileBytes = 2 * kPanel;
+constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;
+
+constexpr int kThreads = 416;     // 8 softmax warps, 1 MMA warp, 4 producer warps
+
+__device__ __forceinline__ void cp16(void* dst, const void* src, bool pred) {
+    const int bytes = pred ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads)
+attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ cache, int num_pages, const __nv_bfloat16* __restrict__ q, int q_stride,
+                         __nv_bfloat16* __restrict__ out, int out_stride, int page_size,
+                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ query_start_loc,
+                         const int* __restrict__ seq_lens, int num_requests, int nq, int nkv, float scale_log2, int window,
+                         int* __restrict__ error_flag) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sQ = base;
+    unsigned char* sK = base + kTileBytes;          // two buffers
+    unsigned char* sV = base + 3 * kTileBytes;      // two buffers
+    unsigned char* sP = base + 5 * kTileBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * kTileBytes);
+    uint64_t* k_full = bars;           // [2]  a key tile has landed
+    uint64_t* v_full = bars + 2;       // [2]  a value tile has landed
+    uint64_t* s_full = bars + 4;       // [2]  S of a tile is in tensor memory
+    uint64_t* p_ready = bars + 6;      //      P of a tile is in shared memory
+    uint64_t* pv_done = bars + 7;      //      O includes a tile
+    uint64_t* k_free = bars + 8;       // [2]  S has read a key buffer (early: keys two tiles ahead can be fetched)
+    uint64_t* v_free = bars + 10;      // [2]  P V has read a value buffer
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    __shared__ int s_req, s_tile, s_abort;
+    __shared__ float s_mx[2][2][128];      // [tile parity][column half][row]: the halves' maxima of a row
+    __shared__ float s_l[2][128];          // [column half][row]: the halves' sums at the end
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.y;
+    const int g = nq / nkv;
+
+    if (tid == 0) {
+        int t = gridDim.x - 1 - blockIdx.x, r = 0;      // later (longer) tiles first
+        for (; r < num_requests; ++r) {
+            const int tiles = ((query_start_loc[r + 1] - query_start_loc[r]) * g + kM - 1) / kM;
+            if (t < tiles) break;
+            t -= tiles;
+        }
+        s_req = r; s_tile = t; s_abort = 0;
+        for (int i = 0; i < 2; ++i) {
+            bar_init(&k_full[i], 128); bar_init(&v_full[i], 128); bar_init(&s_full[i], 1);
+            bar_init(&k_free[i], 1); bar_init(&v_free[i], 1);
+        }
+        bar_init(p_ready, 8);
+        bar_init(pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // stale shared memory must at least be finite: rows of a tile that no page covers are multiplied by P = 0
+    for (int i = tid; i < 4 * kTileBytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(sK)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // before the bulk copies write the same bytes
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int r = s_req;
+    const bool active = r < num_requests;
+
+    int q0 = 0, n = 0, seq_len = 0, row0 = 0, rows_total = 0, num_tiles = 0, k_lo = 0;
+    if (active) {
+        q0 = query_start_loc[r];
+        n = query_start_loc[r + 1] - q0;
+        seq_len = seq_lens[r];
+        rows_total = n * g;
+        row0 = s_tile * kM;
+        const int last_row = min(row0 + kM, rows_total) - 1;
+        const int pos_first = seq_len - n + row0 / g, pos_last = seq_len - n + last_row / g;
+        k_lo = window > 0 ? max(0, pos_first - window + 1) / kN * kN : 0;
+        num_tiles = (pos_last + 1 - k_lo + kN - 1) / kN;
+    }
+
+    if (active && warp < 8) {
+        // ---- the query tile: row = token_local * g + head_in_group, two swizzled 64-column panels ----
+        for (int idx = tid; idx < kM * 16; idx += 256) {
+            const int row = idx >> 4, c = idx & 15;
+            const int grow = row0 + row;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (grow < rows_total) {
+                const int tl = grow / g, hi = grow % g;
+                v = *reinterpret_cast<const uint4*>(q + (size_t)(q0 + tl) * q_stride + (size_t)(kvh * g + hi) * kD + c * 8);
+            }
+            *reinterpret_cast<uint4*>(sQ + (c >> 3) * kPanel + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (active && warp == 8) {
+        // ---- the MMAs: the whole warp walks the loop, lane 0 issues ----
+        auto issue_s = [&](int j) {
+            if (lane != 0) return;
+            const int b = j & 1;
+            const uint64_t qd = desc_kmajor(sQ), kd = desc_kmajor(sK + b * kTileBytes);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint64_t off = (uint64_t)(((k >> 2) * kPanel + (k & 3) * 32) >> 4);
+                mma(tmem + (uint32_t)(b * kN), qd + off, kd + off, idesc(false), k != 0);
+            }
+            commit(&s_full[b]);
+            commit(&k_free[b]);             // the key buffer can be refilled as soon as S has been computed
+        };
+        auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
+            bool ok = bar_wait(bar, parity);
+            if (!ok && lane == 0) { atomicExch(error_flag, code); s_abort = 1; }
+            return __all_sync(0xffffffffu, ok);
+        };
+        bool ok = true;
+        ok = wait_all(&k_full[0], 0, 11);
+        if (ok) { fence_after(); issue_s(0); }
+        for (int j = 0; j < num_tiles && ok; ++j) {
+            if (j + 1 < num_tiles) {
+                ok = wait_all(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 12);
+                if (!ok) break;
+                fence_after();
+                issue_s(j + 1);
+            }
+            ok = wait_all(p_ready, j & 1, 13) && wait_all(&v_full[j & 1], (j >> 1) & 1, 14);
+            if (!ok) break;
+            fence_after();
+            if (lane == 0) {
+                const int b = j & 1;
+                const uint64_t pd = desc_kmajor(sP);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint64_t aoff = (uint64_t)(((k >> 2) * kPanel + (k & 3) * 32) >> 4);
+                    const uint64_t vd = desc_mnmajor(sV + b * kTileBytes + k * 16 * 128, kPanel);
+                    mma(tmem + 2u * kN, pd + aoff, vd, idesc(true), (j | k) != 0);
+                }
+                commit(pv_done);
+                commit(&v_free[b]);         // the value buffer can be refilled
+            }
+            __syncwarp();
+        }
+    } else if (active && warp >= 9) {
+        // ---- producers (128 threads): gather key and value tiles into their swizzled double buffers.  Keys of tile
+        // j+2 are fetched as soon as S(j) has been computed, values after P V(j); a tile is always announced before
+        // the wait for a buffer that its consumer needs it to free. ----
+        const int pt = tid - 288;                       // 0..127
+        const int* table = block_table + (size_t)r * table_stride;
+        const size_t head_stride = (size_t)page_size * kD;
+        const int c = pt & 15, rsub = pt >> 4;          // 16-byte chunk of a row; rows rsub, rsub + 8, ...
+        auto issue = [&](int j, int kv) {
+            const int b = j & 1;
+            unsigned char* dst0 = (kv ? sV : sK) + b * kTileBytes + (c >> 3) * kPanel + ((c & 7) << 4);
+            int key = k_lo + j * kN + rsub;
+            int pidx = key / page_size, off = key - pidx * page_size;      // then stepped without divisions
+            int page = key < seq_len ? table[pidx] : -1;
+#pragma unroll 4
+            for (int pass = 0; pass < 16; ++pass) {
+                const int row = pass * 8 + rsub;
+                const bool valid = key < seq_len && page >= 0 && page < num_pages;
+                const __nv_bfloat16* src = cache + (((size_t)(valid ? page : 0) * 2 + kv) * nkv + kvh) * head_stride +
+                                           (size_t)(valid ? off : 0) * kD + c * 8;
+                cp16(dst0 + row * 128 - ((c & 7) << 4) + (((c & 7) ^ (row & 7)) << 4), src, valid);
+                key += 8;
+                off += 8;
+                if (off >= page_size) {
+                    while (off >= page_size) { off -= page_size; ++pidx; }
+                    page = key < seq_len ? table[pidx] : -1;
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        bool ok = true;
+        // groups in order: K0 V0 K1 V1, then K(j+2) V(j+2) in iteration j
+        issue(0, 0);
+        issue(0, 1);
+        if (num_tiles > 1) { issue(1, 0); issue(1, 1); }
+        asm volatile("cp.async.wait_group 3;" ::: "memory");         // K0 (at most three younger groups pending)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        bar_arrive(&k_full[0]);
+        for (int j = 0; j < num_tiles && ok; ++j) {
+            // A: keys of tile j+1 (only its values, and nothing newer, may still be on the way)
+            if (j + 1 < num_tiles) {
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                bar_arrive(&k_full[(j + 1) & 1]);
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            // B: values of tile j (older than the keys above, so they have landed too)
+            bar_arrive(&v_full[j & 1]);
+            if (j + 2 < num_tiles) {
+                ok = bar_wait(&k_free[j & 1], (j >> 1) & 1);                    // C: S(j) has read the key buffer
+                if (!ok) { atomicExch(error_flag, 18); s_abort = 1; break; }
+                issue(j + 2, 0);
+                ok = bar_wait(&v_free[j & 1], (j >> 1) & 1);                    // D: P V(j) has read the value buffer
+                if (!ok) { atomicExch(error_flag, 19); s_abort = 1; break; }
+                issue(j + 2, 1);
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if (active && warp < 8) {
+        // ---- softmax: two threads per row (TMEM lane), each takes 64 of the 128 columns; warps w and w + 4 share
+        // the lanes 32 * (w % 4) .. + 31 and meet at a named barrier to combine a row's maxima ----
+        const int quarter = warp & 3, half = warp >> 2;
+        const int cb = half * 64;
+        const int row_local = quarter * 32 + lane;
+        const int grow = row0 + row_local;
+        const bool row_ok = grow < rows_total;
+        const int pos = row_ok ? seq_len - n + grow / g : -1;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        auto pair_barrier = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < num_tiles; ++j) {
+            const int b = j & 1;
+            const int key0 = k_lo + j * kN;
+            ok = bar_wait(&s_full[b], (j >> 1) & 1);
+            if (!ok && lane == 0) { atomicExch(error_flag, 15); s_abort = 1; }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
+            if (!ok) break;
+            fence_after();
+            const bool need_mask = key0 + kN - 1 > pos || window > 0;
+            const int hi = pos - key0;                              // columns <= hi are visible ...
+            const int lo = window > 0 ? hi - window : -1;           // ... and > lo
+            // pass 1: the maximum of this thread's half of the row (the scale is positive: applied afterwards)
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                tld32(lane_addr + (uint32_t)(b * kN + cb + c * 32), v);
+                tld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int col = cb + c * 32 + e;
+                        if (col <= hi && col > lo) mx = fmaxf(mx, __uint_as_float(v[e]));
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+                }
+            }
+            s_mx[j & 1][half][row_local] = mx;
+            pair_barrier();
+            mx = fmaxf(s_mx[j & 1][0][row_local], s_mx[j & 1][1][row_local]) * scale_log2;
+            // raise the reference maximum only when it would grow by more than 8 (values stay below 2^8); both
+            // threads of a row see the same numbers and decide alike
+            float corr = 1.f;
+            bool rescale = false;
+            if (mx > m_used + 8.f || (m_used == -INFINITY && mx != -INFINITY)) {
+                corr = m_used == -INFINITY ? 0.f : exp2f(m_used - mx);
+                m_used = mx;
+                l *= corr;
+                rescale = j > 0;
+            }
+            // pass 2: P = 2^(s * scale - m): one fused multiply-add and one ex2 per score, packed two to a register
+            const float m_eff = m_used == -INFINITY ? 0.f : m_used;
+            uint32_t p[32];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                tld32(lane_addr + (uint32_t)(b * kN + cb + c * 32), v);
+                tld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float pe[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        float x = fmaf(__uint_as_float(v[e + u]), scale_log2, -m_eff);
+                        if (need_mask) {
+                            const int col = cb + c * 32 + e + u;
+                            if (!(col <= hi && col > lo)) x = -INFINITY;
+                        }
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe[u]) : "f"(x));
+                    }
+                    l += pe[0] + pe[1];
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(pe[0], pe[1]);
+                    p[c * 16 + e / 2] = *reinterpret_cast<uint32_t*>(&pk);
+                }
+            }
+            // O and the P tile are free once P V of the tile before has finished
+            if (j > 0) {
+                ok = bar_wait(pv_done, (j - 1) & 1);
+                if (!ok && lane == 0) { atomicExch(error_flag, 16); s_abort = 1; }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                fence_after();
+            }
+            if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t v[32];
+                    tld32(lane_addr + (uint32_t)(2 * kN + cb + c * 32), v);
+                    tld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * (rescale ? corr : 1.f));
+                    tst32(lane_addr + (uint32_t)(2 * kN + cb + c * 32), v);
+                }
+                tst_wait();
+            }
+            // this thread's 64 keys are panel `half` of the P tile
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint4 v = make_uint4(p[4 * c], p[4 * c + 1], p[4 * c + 2], p[4 * c + 3]);
+                *reinterpret_cast<uint4*>(sP + half * kPanel + row_local * 128 + ((c ^ (row_local & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            fence_before();
+            __syncwarp();
+            if (lane == 0) bar_arrive(p_ready);
+        }
+        // ---- O / l -> global ----
+        if (ok && num_tiles > 0) {
+            ok = bar_wait(pv_done, (num_tiles - 1) & 1);
+            if (!ok && lane == 0) { atomicExch(error_flag, 17); s_abort = 1; }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        s_l[half][row_local] = l;
+        pair_barrier();
+        if (ok && num_tiles > 0) {
+            fence_after();
+            l = s_l[0][row_local] + s_l[1][row_local];
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = nullptr;
+            if (row_ok) {
+                const int tl = grow / g, hi = grow % g;
+                dst = out + (size_t)(q0 + tl) * out_stride + (size_t)(kvh * g + hi) * kD + cb;
+            }
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                tld32(lane_addr + (uint32_t)(2 * kN + cb + c * 32), v);
+                tld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 pk;
+                        __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
+                        __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+                        __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
+                        __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
+                        pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
+                        pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + e) = pk;
+                    }
+                }
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+}
+
+}  // namespace fa
+}  // namespace cib
+
+using namespace cib;
+
+extern "C" int cib_attention_tcgen05_supports(int head_dim, int nq, int nkv, int page_size) {
+    if (head_dim != 128 || nkv <= 0 || nq % nkv != 0) return 0;
+    const int g = nq / nkv;
+    return 128 % g == 0 && page_size >= 1;
+}
+
+// num_tiles = sum over requests of ceil(tokens_r * (nq / nkv) / 128).  error_flag: one zero int in device memory.
+extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int out_stride, const void* cache, int num_pages,
+                                     int page_size, const int* block_table, int table_stride, const int* query_start_loc,
+                                     const int* seq_lens, int num_requests, int num_tiles, int nq, int nkv, int head_dim,
+                                     float scale, int window, int* error_flag, cudaStream_t stream) {
+    CIB_REQUIRE(cib_attention_tcgen05_supports(head_dim, nq, nkv, page_size),
+                "attention_tcgen05: head_dim %d, %d/%d heads, page size %d are not taken (head size 128, heads per kv head dividing 128)",
+                head_dim, nq, nkv, page_size);
+    CIB_REQUIRE(num_requests >= 0 && num_tiles >= 0 && nkv <= 65535 && num_pages > 0 && table_stride > 0, "attention_tcgen05: bad sizes");
+    CIB_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && out_stride % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)cache % 16) == 0,
+                "attention_tcgen05: rows must be 16-byte aligned");
+    CIB_REQUIRE(error_flag != nullptr, "attention_tcgen05: error flag missing");
+    if (num_requests == 0 || num_tiles == 0) return 0;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(fa::attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::kSmemBytes);
+        if (e != cudaSuccess) {
+            set_error("attention_tcgen05: cannot raise shared memory to %d: %s", fa::kSmemBytes, cudaGetErrorString(e));
+            return -2;
+        }
+        configured = true;
+    }
+    dim3 grid(num_tiles, nkv);
+    fa::attention_tcgen05_kernel<<<grid, fa::kThreads, fa::kSmemBytes, stream>>>(
+        (const __nv_bfloat16*)cache, num_pages, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, page_size, block_table, table_stride,
+        query_start_loc, seq_lens, num_requests, nq, nkv, scale * 1.4426950408889634f, window, error_flag);
+    CIB_LAUNCH_CHECK("attention_tcgen05");
+    return 0;
+}

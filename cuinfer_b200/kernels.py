@@ -74,6 +74,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
         "cib_paged_attention_decode_fused": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I,
                                              _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P],
+        "cib_attention_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
         "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P],
         "cib_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
@@ -87,6 +88,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.cib_paged_attention_decode_supports.restype = _I
     lib.cib_gemm_tcgen05_supports.argtypes = [_I, _I, _I]
     lib.cib_gemm_tcgen05_supports.restype = _I
+    lib.cib_attention_tcgen05_supports.argtypes = [_I, _I, _I, _I]
+    lib.cib_attention_tcgen05_supports.restype = _I
     lib.cib_gemm_skinny_supports.argtypes = [_I, _I, _I, _I]
     lib.cib_gemm_skinny_supports.restype = _I
     lib.cib_paged_attention_prefill_supports.argtypes = [_I, _I, _I]
@@ -499,6 +502,34 @@ def check_error_flags() -> None:
         if code:
             flag.zero_()
             raise KernelError(f"a kernel on cuda:{index} gave up waiting on a barrier (code {code}); its results are invalid")
+
+
+def attention_tcgen05_supports(head_dim: int, num_q_heads: int, num_kv_heads: int, page_size: int) -> bool:
+    return bool(library().cib_attention_tcgen05_supports(head_dim, num_q_heads, num_kv_heads, page_size))
+
+
+def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                      query_start_loc: torch.Tensor, seq_lens: torch.Tensor, query_lens_host, num_q_heads: int,
+                      num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """bfloat16 attention for prompt portions on tcgen05 tensor cores (head size 128): scores and output
+    accumulate in tensor memory, keys and values come page by page through a 5-D TMA tensor map."""
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_tcgen05: bfloat16 only")
+    if q.stride(1) != 1 or out.stride(1) != 1 or out.shape != (T, num_q_heads * head_dim) or not cache.is_contiguous():
+        raise KernelError("attention_tcgen05: q/out rows must be dense, out [T, nq*d], cache contiguous")
+    g = num_q_heads // num_kv_heads
+    tiles = sum((n * g + 127) // 128 for n in query_lens_host)
+    rc = library().cib_attention_tcgen05(
+        _cuda(q, "q", contiguous=False), q.stride(0), _cuda(out, "out", contiguous=False), out.stride(0),
+        _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
+        block_table.stride(0), _cuda(query_start_loc, "query_start_loc", torch.int32),
+        _cuda(seq_lens, "seq_lens", torch.int32), len(query_lens_host), tiles, num_q_heads, num_kv_heads, head_dim,
+        float(scale), int(window), _error_flag(q.device).data_ptr(), _stream())
+    _check(rc, "attention_tcgen05")
+    global _flagged_launches
+    _flagged_launches += 1
+    _count()
 
 
 def gemm_tcgen05_supports(M: int, N: int, K: int) -> bool:

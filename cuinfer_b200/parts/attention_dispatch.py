@@ -1,14 +1,21 @@
 """Choice of the paged-attention kernel for a step.
 
-float32 always runs the all-sizes kernel.  bfloat16 runs the tensor-core kernels where they take the
-head size and falls back to the all-sizes kernel otherwise; a size no kernel takes raises there.
+float32 always runs the all-sizes kernel.  bfloat16: a step of single decoded tokens runs the split-KV kernel; any
+other step runs the tcgen05 kernel (head size 128, heads per kv head dividing 128) or the mma.sync kernel (head
+size 64 or 128); other head sizes fall back to the all-sizes kernel.  ``CUINFER_B200_ATTENTION=mma`` keeps prompt
+portions off the tcgen05 kernel (for comparisons).
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
 from .. import kernels
 from .context import PagedKV, StepContext
+
+
+_FORCE_MMA = os.environ.get("CUINFER_B200_ATTENTION", "") == "mma"
 
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepContext, num_heads: int,
@@ -18,6 +25,13 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: Step
         splits = kernels.decode_splits(ctx.num_requests, num_kv_heads, max(1, ctx.max_seq_len))
         kernels.paged_attention_decode(qkv, out, kv.cache, kv.group.block_table, ctx.seq_lens, num_heads,
                                        num_kv_heads, head_dim, scale, window, splits)
+        return
+    if qkv.dtype == torch.bfloat16 and not _FORCE_MMA and kernels.attention_tcgen05_supports(
+            head_dim, num_heads, num_kv_heads, kv.group.page_size) and out.stride(0) % 8 == 0 and qkv.stride(0) % 8 == 0:
+        starts = ctx.query_start_loc_host
+        lens = [starts[i + 1] - starts[i] for i in range(ctx.num_requests)]
+        kernels.attention_tcgen05(qkv, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens, lens,
+                                  num_heads, num_kv_heads, head_dim, scale, window)
         return
     if qkv.dtype == torch.bfloat16 and kernels.paged_attention_prefill_supports(head_dim, num_heads, num_kv_heads):
         starts = ctx.query_start_loc_host

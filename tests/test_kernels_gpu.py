@@ -412,6 +412,28 @@ def test_paged_attention_decode_fused_equals_the_two_kernels(nq, nkv, d, ps, rot
     assert torch.equal(cache_b.cpu(), cache_a.cpu())
 
 
+@pytest.mark.parametrize("nq, nkv, ps", [(16, 8, 16), (8, 1, 32), (4, 4, 5), (32, 2, 128)])
+@pytest.mark.parametrize("window", [None, 200])
+def test_attention_tcgen05(nq, nkv, ps, window):
+    """The tensor-memory attention kernel on portions of every length beside decoded tokens."""
+    k = _k()
+    d = 128
+    assert k.attention_tcgen05_supports(d, nq, nkv, ps)
+    lens = [1, 37, 64, 130, 5, 300, 257, 1000, 128, 640]
+    new = [1, 37, 1, 17, 2, 300, 129, 1, 128, 513]
+    case = attention_case(torch.bfloat16, nq, nkv, d, lens, new, ps, seed=80, sharp=True)
+    scale = 1.0 / math.sqrt(d)
+    T = sum(new)
+    out = torch.full((T, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        k.attention_tcgen05(case["wide"].to(DEV), out, case["cache"].to(DEV), case["bt"].to(DEV), i32(case["qsl"]),
+                            i32(lens), new, nq, nkv, d, scale, window or 0)
+        k.check_error_flags()
+    close(out, attention_reference(case, lens, new, scale, window), 1.5e-2)
+    assert not k.attention_tcgen05_supports(64, 8, 8, 16) and not k.attention_tcgen05_supports(128, 12, 4, 16)
+
+
 def test_paged_attention_decode_refuses_other_sizes():
     k = _k()
     assert not k.paged_attention_decode_supports(48, 6, 3)
