@@ -115,6 +115,30 @@ def gemm(args) -> dict:
             "GBps": round((N * K + M * K + M * N) * 2 / ms / 1e6, 1), "TFLOPs": round(2.0 * M * N * K / ms / 1e9, 2)}
 
 
+def rope(args) -> dict:
+    """Per-head norm, rotary encoding and cache write of ``--tokens`` packed qkv rows."""
+    T, nq, nkv, d, ps = args.tokens, args.q_heads, args.kv_heads, args.head_dim, args.page_size
+    dev = "cuda:0"
+    copies = max(1, args.copies)
+    pages = (T + ps - 1) // ps
+    qkv = torch.randn(copies, T, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16)
+    cache = torch.zeros(copies * pages, 2, nkv, ps, d, device=dev, dtype=torch.bfloat16)
+    positions = torch.arange(T, device=dev, dtype=torch.int32)
+    slots = torch.randperm(pages, device=dev).repeat_interleave(ps)[:T].to(torch.int32) * ps + positions % ps
+    qw = torch.ones(d, device=dev, dtype=torch.bfloat16)
+    inv = 1.0 / torch.pow(torch.tensor(1e6), torch.arange(d // 2, dtype=torch.float32) * 2.0 / d)
+    ang = torch.arange(T, dtype=torch.float32)[:, None] * inv[None, :]
+    table = torch.stack((torch.cos(ang), torch.sin(ang)), -1).contiguous().to(dev)
+
+    def run(i):
+        c = i % copies
+        kernels.qk_norm_rope_kv_write(qkv[c], positions, slots + c * pages * ps, qw, qw, 1e-6, table, d, cache, nq, nkv, d)
+
+    ms = _time(run, args.iters)
+    moved = T * (nq + 2 * nkv) * d * 2 * 2
+    return {"kernel": "qk_norm_rope_kv_write", "tokens": T, "ms": round(ms, 4), "GBps": round(moved / ms / 1e6, 1)}
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="python -m cuinfer_b200.bench_kernels")
     sub = p.add_subparsers(dest="kernel", required=True)
@@ -137,6 +161,14 @@ def main(argv=None) -> int:
     f.add_argument("--page-size", type=int, default=16)
     f.add_argument("--impl", default="mma", choices=["mma", "tcgen05"])
     f.add_argument("--iters", type=int, default=10)
+    ro = sub.add_parser("rope", help=rope.__doc__)
+    ro.add_argument("--tokens", type=int, default=2048)
+    ro.add_argument("--q-heads", type=int, default=16)
+    ro.add_argument("--kv-heads", type=int, default=8)
+    ro.add_argument("--head-dim", type=int, default=128)
+    ro.add_argument("--page-size", type=int, default=16)
+    ro.add_argument("--copies", type=int, default=8)
+    ro.add_argument("--iters", type=int, default=16)
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=8)
     g.add_argument("--n", type=int, default=4096)
@@ -147,7 +179,7 @@ def main(argv=None) -> int:
     g.add_argument("--copies", type=int, default=8)
     g.add_argument("--iters", type=int, default=20)
     args = p.parse_args(argv)
-    result = {"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm}[args.kernel](args)
+    result = {"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm, "rope": rope}[args.kernel](args)
     print(json.dumps(result))
     return 0
 

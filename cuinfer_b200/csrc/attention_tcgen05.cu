@@ -5,9 +5,11 @@
 // Blackwell's own path instead of mma.sync:
 //
 //   * a CTA owns a 128-row query tile (128 / g tokens x g heads of one kv head) and walks over 128-key tiles;
-//   * keys and values are gathered page by page by four producer warps with 16-byte `cp.async` copies that write
-//     the 128-byte-swizzled layout the tensor cores read (a 16-slot page is a 2 KB box per 64 columns: as TMA boxes
-//     that small the copies were issue-bound, 32 per tile), double-buffered, handed over through mbarriers;
+//   * keys and values come page by page through TMA (`cp.async.bulk.tensor.2d`, one box of 64 columns x one page per
+//     copy, 128-byte swizzle: the layout the tensor cores read), issued by the lanes of one producer warp in parallel,
+//     double-buffered, completion counted in bytes on mbarriers.  (Copies issued by ordinary loads or `cp.async` kept
+//     too few bytes in flight per SM: a tile took longer to arrive than its softmax takes.)  The page size must be a
+//     power of two of at least 8 slots, so that a box starts on a 1024-byte swizzle atom;
 //   * S = Q K^T and O += P V are `tcgen05.mma.cta_group::1.kind::f16` with accumulators in tensor memory: two S
 //     buffers (128 columns each) and O (128 columns); K is a K-major operand, V an MN-major one, straight from the
 //     page layout;
@@ -20,6 +22,7 @@
 // and returns.
 #include "common.cuh"
 
+#include <cuda.h>
 
 namespace cib {
 namespace fa {
@@ -101,15 +104,16 @@ __device__ __forceinline__ void tst_wait() { asm volatile("tcgen05.wait::st.sync
 constexpr int kTileBytes = 2 * kPanel;
 constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;
 
-constexpr int kThreads = 416;     // 8 softmax warps, 1 MMA warp, 4 producer warps
+constexpr int kThreads = 352;     // 8 softmax warps, 1 MMA warp, a producer warp for keys and one for values
 
-__device__ __forceinline__ void cp16(void* dst, const void* src, bool pred) {
-    const int bytes = pred ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s32(dst)), "l"(src), "r"(bytes) : "memory");
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(s32(smem_dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1) : "memory");
 }
 
 __global__ void __launch_bounds__(kThreads)
-attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ cache, int num_pages, const __nv_bfloat16* __restrict__ q, int q_stride,
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pages, const __nv_bfloat16* __restrict__ q, int q_stride,
                          __nv_bfloat16* __restrict__ out, int out_stride, int page_size,
                          const int* __restrict__ block_table, int table_stride, const int* __restrict__ query_start_loc,
                          const int* __restrict__ seq_lens, int num_requests, int nq, int nkv, float scale_log2, int window,
@@ -121,7 +125,7 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ cache, int num_pages,
     unsigned char* sV = base + 3 * kTileBytes;      // two buffers
     unsigned char* sP = base + 5 * kTileBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * kTileBytes);
-    uint64_t* k_full = bars;           // [2]  a key tile has landed
+    uint64_t* k_full = bars;           // [2]  a key tile has landed (bytes counted)
     uint64_t* v_full = bars + 2;       // [2]  a value tile has landed
     uint64_t* s_full = bars + 4;       // [2]  S of a tile is in tensor memory
     uint64_t* p_ready = bars + 6;      //      P of a tile is in shared memory
@@ -146,7 +150,7 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ cache, int num_pages,
         }
         s_req = r; s_tile = t; s_abort = 0;
         for (int i = 0; i < 2; ++i) {
-            bar_init(&k_full[i], 128); bar_init(&v_full[i], 128); bar_init(&s_full[i], 1);
+            bar_init(&k_full[i], 1); bar_init(&v_full[i], 1); bar_init(&s_full[i], 1);
             bar_init(&k_free[i], 1); bar_init(&v_free[i], 1);
         }
         bar_init(p_ready, 8);
@@ -228,6 +232,22 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ cache, int num_pages,
             }
             ok = wait_all(p_ready, j & 1, 13) && wait_all(&v_full[j & 1], (j >> 1) & 1, 14);
             if (!ok) break;
+            {
+                // the last page of the request came whole: value rows past its last token may hold anything, and
+                // 0 x NaN is NaN, so they are cleared (their columns of P are 0)
+                const int valid_rows = seq_len - (k_lo + j * kN);
+                if (valid_rows < kN) {
+                    const int box_rows = min(page_size, kN);
+                    const int end = min(kN, (valid_rows + box_rows - 1) / box_rows * box_rows);
+                    unsigned char* vb = sV + (j & 1) * kTileBytes;
+                    for (int idx = valid_rows * 16 + lane; idx < end * 16; idx += 32) {
+                        const int row = idx >> 4, c = idx & 15;
+                        *reinterpret_cast<uint4*>(vb + (c >> 3) * kPanel + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                }
+            }
             fence_after();
             if (lane == 0) {
                 const int b = j & 1;
@@ -244,65 +264,53 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ cache, int num_pages,
             __syncwarp();
         }
     } else if (active && warp >= 9) {
-        // ---- producers (128 threads): gather key and value tiles into their swizzled double buffers.  Keys of tile
-        // j+2 are fetched as soon as S(j) has been computed, values after P V(j); a tile is always announced before
-        // the wait for a buffer that its consumer needs it to free. ----
-        const int pt = tid - 288;                       // 0..127
+        // ---- producer warps (9: keys, 10: values): a lane issues one TMA copy per (page of the tile, 64-column panel); keys of tile j+2 as
+        // soon as S(j) has read the buffer, values after P V(j).  Rows of a tile past the request's last page are not
+        // copied: their columns of S are masked and P is 0 there.  A page number outside the pool turns into a row
+        // outside the tensor map, which reads as zeros and still counts its bytes. ----
         const int* table = block_table + (size_t)r * table_stride;
-        const size_t head_stride = (size_t)page_size * kD;
-        const int c = pt & 15, rsub = pt >> 4;          // 16-byte chunk of a row; rows rsub, rsub + 8, ...
-        auto issue = [&](int j, int kv) {
-            const int b = j & 1;
-            unsigned char* dst0 = (kv ? sV : sK) + b * kTileBytes + (c >> 3) * kPanel + ((c & 7) << 4);
-            int key = k_lo + j * kN + rsub;
-            int pidx = key / page_size, off = key - pidx * page_size;      // then stepped without divisions
-            int page = key < seq_len ? table[pidx] : -1;
-#pragma unroll 4
-            for (int pass = 0; pass < 16; ++pass) {
-                const int row = pass * 8 + rsub;
-                const bool valid = key < seq_len && page >= 0 && page < num_pages;
-                const __nv_bfloat16* src = cache + (((size_t)(valid ? page : 0) * 2 + kv) * nkv + kvh) * head_stride +
-                                           (size_t)(valid ? off : 0) * kD + c * 8;
-                cp16(dst0 + row * 128 - ((c & 7) << 4) + (((c & 7) ^ (row & 7)) << 4), src, valid);
-                key += 8;
-                off += 8;
-                if (off >= page_size) {
-                    while (off >= page_size) { off -= page_size; ++pidx; }
-                    page = key < seq_len ? table[pidx] : -1;
-                }
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+        const int box_rows = min(page_size, kN);
+        const int boxes = kN / box_rows;
+        const long long total_rows = (long long)num_pages * 2 * nkv * page_size;
+        // a tile has at most 32 boxes (16 pages of 8 slots x 2 panels): lane = box * 2 + panel.  The page number of
+        // a lane's box is fetched a tile ahead, so that no copy waits for a round trip to the table.
+        const int box = lane >> 1, panel = lane & 1;
+        int page = -1;
+        auto lookup = [&](int t) {
+            const int key = k_lo + t * kN + box * box_rows;
+            page = t < num_tiles && box < boxes && key < seq_len ? __ldg(table + key / page_size) : -1;
         };
-        bool ok = true;
-        // groups in order: K0 V0 K1 V1, then K(j+2) V(j+2) in iteration j
-        issue(0, 0);
-        issue(0, 1);
-        if (num_tiles > 1) { issue(1, 0); issue(1, 1); }
-        asm volatile("cp.async.wait_group 3;" ::: "memory");         // K0 (at most three younger groups pending)
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        bar_arrive(&k_full[0]);
-        for (int j = 0; j < num_tiles && ok; ++j) {
-            // A: keys of tile j+1 (only its values, and nothing newer, may still be on the way)
-            if (j + 1 < num_tiles) {
-                asm volatile("cp.async.wait_group 1;" ::: "memory");
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                bar_arrive(&k_full[(j + 1) & 1]);
-            } else {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        auto fill = [&](int t, int kv) {
+            const int b = t & 1;
+            const int key0 = k_lo + t * kN;
+            uint64_t* bar = kv ? &v_full[b] : &k_full[b];
+            const int nvalid = min(boxes, max(0, (seq_len - key0 + box_rows - 1) / box_rows));
+            if (lane == 0) bar_expect(bar, (uint32_t)(nvalid * 2 * box_rows * 128));
+            __syncwarp();
+            if (box < nvalid) {
+                const int off = (key0 + box * box_rows) % page_size;        // not 0 only for pages longer than a tile
+                const long long row = page >= 0 && page < num_pages
+                                          ? (((long long)page * 2 + kv) * nkv + kvh) * page_size + off : total_rows;
+                tma_load_2d((kv ? sV : sK) + b * kTileBytes + panel * kPanel + box * box_rows * 128, &kv_map, bar, panel * 64, (int)row);
             }
-            // B: values of tile j (older than the keys above, so they have landed too)
-            bar_arrive(&v_full[j & 1]);
-            if (j + 2 < num_tiles) {
-                ok = bar_wait(&k_free[j & 1], (j >> 1) & 1);                    // C: S(j) has read the key buffer
-                if (!ok) { atomicExch(error_flag, 18); s_abort = 1; break; }
-                issue(j + 2, 0);
-                ok = bar_wait(&v_free[j & 1], (j >> 1) & 1);                    // D: P V(j) has read the value buffer
-                if (!ok) { atomicExch(error_flag, 19); s_abort = 1; break; }
-                issue(j + 2, 1);
-            }
+        };
+        auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
+            bool ok = bar_wait(bar, parity);
+            if (!ok && lane == 0) { atomicExch(error_flag, code); s_abort = 1; }
+            return __all_sync(0xffffffffu, ok);
+        };
+        const int kv = warp - 9;
+        uint64_t* free_bar = kv ? v_free : k_free;
+        lookup(0);
+        fill(0, kv);
+        lookup(1);
+        if (num_tiles > 1) fill(1, kv);
+        lookup(2);
+        for (int j = 0; j + 2 < num_tiles; ++j) {
+            if (!wait_all(&free_bar[j & 1], (j >> 1) & 1, 18 + kv)) break;      // S(j) / P V(j) has read the buffer
+            fill(j + 2, kv);
+            lookup(j + 3);
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (active && warp < 8) {
         // ---- softmax: two threads per row (TMEM lane), each takes 64 of the 128 columns; warps w and w + 4 share
         // the lanes 32 * (w % 4) .. + 31 and meet at a named barrier to combine a row's maxima ----
@@ -327,24 +335,22 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ cache, int num_pages,
             const bool need_mask = key0 + kN - 1 > pos || window > 0;
             const int hi = pos - key0;                              // columns <= hi are visible ...
             const int lo = window > 0 ? hi - window : -1;           // ... and > lo
-            // pass 1: the maximum of this thread's half of the row (the scale is positive: applied afterwards)
+            // this thread's 64 scores, read from tensor memory once; masked ones become -inf here, so that the
+            // maximum (the scale is positive: applied afterwards) and the exponentials need no second look at the mask
+            uint32_t v[64];
+            tld32(lane_addr + (uint32_t)(b * kN + cb), *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            tld32(lane_addr + (uint32_t)(b * kN + cb + 32), *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            tld_wait();
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tld32(lane_addr + (uint32_t)(b * kN + cb + c * 32), v);
-                tld_wait();
-                if (need_mask) {
+            if (need_mask) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int col = cb + c * 32 + e;
-                        if (col <= hi && col > lo) mx = fmaxf(mx, __uint_as_float(v[e]));
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+                for (int e = 0; e < 64; ++e) {
+                    const int col = cb + e;
+                    if (!(col <= hi && col > lo)) v[e] = __float_as_uint(-INFINITY);
                 }
             }
+#pragma unroll
+            for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
             s_mx[j & 1][half][row_local] = mx;
             pair_barrier();
             mx = fmaxf(s_mx[j & 1][0][row_local], s_mx[j & 1][1][row_local]) * scale_log2;
@@ -362,26 +368,16 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ cache, int num_pages,
             const float m_eff = m_used == -INFINITY ? 0.f : m_used;
             uint32_t p[32];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tld32(lane_addr + (uint32_t)(b * kN + cb + c * 32), v);
-                tld_wait();
+            for (int e = 0; e < 64; e += 2) {
+                float pe[2];
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    float pe[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        float x = fmaf(__uint_as_float(v[e + u]), scale_log2, -m_eff);
-                        if (need_mask) {
-                            const int col = cb + c * 32 + e + u;
-                            if (!(col <= hi && col > lo)) x = -INFINITY;
-                        }
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe[u]) : "f"(x));
-                    }
-                    l += pe[0] + pe[1];
-                    __nv_bfloat162 pk = __floats2bfloat162_rn(pe[0], pe[1]);
-                    p[c * 16 + e / 2] = *reinterpret_cast<uint32_t*>(&pk);
+                for (int u = 0; u < 2; ++u) {
+                    const float x = fmaf(__uint_as_float(v[e + u]), scale_log2, -m_eff);
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe[u]) : "f"(x));
                 }
+                l += pe[0] + pe[1];
+                __nv_bfloat162 pk = __floats2bfloat162_rn(pe[0], pe[1]);
+                p[e / 2] = *reinterpret_cast<uint32_t*>(&pk);
             }
             // O and the P tile are free once P V of the tile before has finished
             if (j > 0) {
@@ -465,7 +461,7 @@ using namespace cib;
 extern "C" int cib_attention_tcgen05_supports(int head_dim, int nq, int nkv, int page_size) {
     if (head_dim != 128 || nkv <= 0 || nq % nkv != 0) return 0;
     const int g = nq / nkv;
-    return 128 % g == 0 && page_size >= 1;
+    return 128 % g == 0 && page_size >= 8 && (page_size & (page_size - 1)) == 0;
 }
 
 // num_tiles = sum over requests of ceil(tokens_r * (nq / nkv) / 128).  error_flag: one zero int in device memory.
@@ -474,13 +470,20 @@ extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int
                                      const int* seq_lens, int num_requests, int num_tiles, int nq, int nkv, int head_dim,
                                      float scale, int window, int* error_flag, cudaStream_t stream) {
     CIB_REQUIRE(cib_attention_tcgen05_supports(head_dim, nq, nkv, page_size),
-                "attention_tcgen05: head_dim %d, %d/%d heads, page size %d are not taken (head size 128, heads per kv head dividing 128)",
+                "attention_tcgen05: head_dim %d, %d/%d heads, page size %d are not taken (head size 128, heads per kv head dividing 128, pages of 8, 16, 32, ... slots)",
                 head_dim, nq, nkv, page_size);
     CIB_REQUIRE(num_requests >= 0 && num_tiles >= 0 && nkv <= 65535 && num_pages > 0 && table_stride > 0, "attention_tcgen05: bad sizes");
     CIB_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && out_stride % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)cache % 16) == 0,
                 "attention_tcgen05: rows must be 16-byte aligned");
     CIB_REQUIRE(error_flag != nullptr, "attention_tcgen05: error flag missing");
     if (num_requests == 0 || num_tiles == 0) return 0;
+    // the cache as rows of one head's slot: [pages * 2 * kv heads * page_size, 128]; a box is one page x 64 columns
+    const long long total_rows = (long long)num_pages * 2 * nkv * page_size;
+    CIB_REQUIRE(total_rows < (1ll << 31), "attention_tcgen05: %lld cache rows do not fit a 32-bit coordinate", total_rows);
+    CUtensorMap kv_map;
+    if (encode_tensor_map_bf16_2d(&kv_map, cache, (unsigned long long)total_rows, fa::kD, fa::kD, 64,
+                                  page_size < fa::kN ? page_size : fa::kN, "attention_tcgen05") != 0)
+        return -1;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fa::attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::kSmemBytes);
@@ -492,7 +495,7 @@ extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int
     }
     dim3 grid(num_tiles, nkv);
     fa::attention_tcgen05_kernel<<<grid, fa::kThreads, fa::kSmemBytes, stream>>>(
-        (const __nv_bfloat16*)cache, num_pages, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, page_size, block_table, table_stride,
+        kv_map, num_pages, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, page_size, block_table, table_stride,
         query_start_loc, seq_lens, num_requests, nq, nkv, scale * 1.4426950408889634f, window, error_flag);
     CIB_LAUNCH_CHECK("attention_tcgen05");
     return 0;

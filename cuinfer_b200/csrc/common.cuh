@@ -20,6 +20,12 @@ constexpr int kWarp = 32;
 // ---- error reporting -------------------------------------------------------------------
 void set_error(const char* fmt, ...);
 
+// A 2-D tensor map over bfloat16 rows (`cols` elements, `ld` elements apart) with boxes of box_cols x box_rows,
+// 128-byte swizzle, zero fill outside.  `map` points at a CUtensorMap (kept opaque here so that only the files that
+// issue TMA copies include the driver header).  0, or -1 with the error text set.
+int encode_tensor_map_bf16_2d(void* map, const void* base, unsigned long long rows, int cols, int ld, int box_cols,
+                              int box_rows, const char* who);
+
 #define CIB_REQUIRE(cond, ...)            \
     do {                                  \
         if (!(cond)) {                    \

@@ -83,6 +83,245 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int row_stride
     for (int i = rotary_dim + lane; i < d; i += 32) dst[i] = from_f32<T>(sv[i]);
 }
 
+// The common case — the encoding spans the whole head (or is absent) and the head size is a multiple of 32 —
+// without loops: a lane owns E = d / 32 neighbouring values, every load is issued before anything is used (one
+// memory latency per head instead of one per pass), the partner of a rotation pair sits 16 lanes away.
+template <typename T, int E>
+struct alignas(sizeof(T) * E > 16 ? 16 : sizeof(T) * E) LaneValues {
+    T v[E];
+};
+
+template <typename T, int E>
+__global__ void qk_norm_rope_kv_write_fast_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                                  const int* __restrict__ slot_mapping, AnyVec q_weight, AnyVec k_weight,
+                                                  int has_norm, float eps, const float* __restrict__ rope_table,
+                                                  int has_rope, int max_positions, T* __restrict__ cache, int num_pages,
+                                                  int page_size, int nq, int nkv, int write_cache) {
+    constexpr int D = E * 32;
+    griddep_launch();
+    griddep_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int head = blockIdx.y * kRopeWarps + warp;
+    const int total_heads = write_cache ? nq + 2 * nkv : nq;
+    if (head >= total_heads) return;
+    T* src = qkv + (size_t)t * row_stride + (size_t)head * D + lane * E;
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    const int kvh = is_q ? 0 : (is_k ? head - nq : head - nq - nkv);
+    T* dst = src;
+    if (!is_q) {
+        const int slot = slot_mapping[t];
+        if (slot < 0) return;
+        const int page = slot / page_size, off = slot - page * page_size;
+        if (page >= num_pages) return;
+        dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * D + lane * E;
+    }
+    using Vec = LaneValues<T, E>;
+    const Vec rawv = *reinterpret_cast<const Vec*>(src);
+    const T* raw = rawv.v;
+    if (!is_q && !is_k) {
+        *reinterpret_cast<Vec*>(dst) = rawv;
+        return;
+    }
+    float x[E], wv[E], cs[2 * E];
+    const AnyVec& w = is_q ? q_weight : k_weight;
+    if (has_norm) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) wv[e] = w[lane * E + e];
+    }
+    if (has_rope) {
+        int pos = positions[t];
+        pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
+        const float* tp = rope_table + (size_t)pos * D + 2 * ((lane & 15) * E);
+        if constexpr (E % 2 == 0) {
+#pragma unroll
+            for (int e = 0; e < E / 2; ++e) {
+                const float4 v = reinterpret_cast<const float4*>(tp)[e];
+                cs[4 * e] = v.x, cs[4 * e + 1] = v.y, cs[4 * e + 2] = v.z, cs[4 * e + 3] = v.w;
+            }
+        } else {
+            const float2 v = *reinterpret_cast<const float2*>(tp);
+            cs[0] = v.x, cs[1] = v.y;
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) x[e] = to_f32(raw[e]);
+    if (has_norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) ss += x[e] * x[e];
+        ss = warp_sum(ss);
+        const float factor = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int e = 0; e < E; ++e) x[e] = x[e] * factor * wv[e];
+    }
+    if (has_rope) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+            const float c = cs[2 * e], sn = cs[2 * e + 1];
+            x[e] = lane < 16 ? x[e] * c - other * sn : x[e] * c + other * sn;
+        }
+    }
+    Vec outv;
+#pragma unroll
+    for (int e = 0; e < E; ++e) outv.v[e] = from_f32<T>(x[e]);
+    *reinterpret_cast<Vec*>(dst) = outv;
+}
+
+// The same for many tokens (prompt portions), where the kernel above is bound by its instruction count (a lane
+// handles four values of a head).  Here a head is spread over L = d / 8 lanes; a lane holds four values of the
+// first half of the head and their four rotation partners of the second half, so that the rotation needs no
+// exchange; a warp takes up to 4 x (32 / L) heads of one token, issues all their loads first, and computes what
+// depends on the token only (cache slot, table row, weights) once.
+template <typename T>
+struct alignas(sizeof(T) * 4) Four {
+    T v[4];
+};
+
+constexpr int kBulkWarps = 8;
+constexpr int kBulkPasses = 4;
+
+template <typename T, int L>
+__global__ void __launch_bounds__(kBulkWarps * 32)
+qk_norm_rope_kv_write_bulk_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                  const int* __restrict__ slot_mapping, AnyVec q_weight, AnyVec k_weight, int has_norm,
+                                  float eps, const float* __restrict__ rope_table, int has_rope, int max_positions,
+                                  T* __restrict__ cache, int num_pages, int page_size, int nq, int nkv, int write_cache,
+                                  int num_tokens) {
+    constexpr int D = 8 * L, HPP = 32 / L;                    // heads per pass
+    using Vec = Four<T>;
+    griddep_launch();
+    griddep_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_heads = write_cache ? nq + 2 * nkv : nq;
+    const int groups = (total_heads + HPP * kBulkPasses - 1) / (HPP * kBulkPasses);
+    const int wg = blockIdx.x * kBulkWarps + warp;
+    const int t = wg / groups;
+    if (t >= num_tokens) return;
+    const int head_base = (wg - t * groups) * HPP * kBulkPasses;
+    const int sub = lane / L, li = lane % L;
+    T* row = qkv + (size_t)t * row_stride;
+    // this lane's eight values of each head: [4 li, 4 li + 4) and the same range of the second half
+    Vec lo[kBulkPasses], hi[kBulkPasses];
+#pragma unroll
+    for (int p = 0; p < kBulkPasses; ++p) {
+        const int head = head_base + p * HPP + sub;
+        if (head < total_heads) {
+            const T* src = row + (size_t)head * D + 4 * li;
+            lo[p] = *reinterpret_cast<const Vec*>(src);
+            hi[p] = *reinterpret_cast<const Vec*>(src + D / 2);
+        }
+    }
+    // what depends on the token only
+    T* cache_row = nullptr;                                   // slot `off` of kv head 0 of the key half of the page
+    if (write_cache) {
+        const int slot = slot_mapping[t];
+        if (slot >= 0) {
+            const int page = slot / page_size, off = slot - page * page_size;
+            if (page < num_pages) cache_row = cache + ((size_t)page * 2 * nkv * page_size + off) * D;
+        }
+    }
+    float cs[8];
+    if (has_rope) {
+        int pos = positions[t];
+        pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
+        const float4* tp = reinterpret_cast<const float4*>(rope_table + (size_t)pos * D + 8 * li);
+        const float4 a = tp[0], b = tp[1];
+        cs[0] = a.x, cs[1] = a.y, cs[2] = a.z, cs[3] = a.w, cs[4] = b.x, cs[5] = b.y, cs[6] = b.z, cs[7] = b.w;
+    }
+    float wq[8], wk[8];
+    if (has_norm) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            wq[e] = q_weight[4 * li + e], wq[4 + e] = q_weight[D / 2 + 4 * li + e];
+            wk[e] = k_weight[4 * li + e], wk[4 + e] = k_weight[D / 2 + 4 * li + e];
+        }
+    }
+#pragma unroll
+    for (int p = 0; p < kBulkPasses; ++p) {
+        const int head = head_base + p * HPP + sub;
+        const bool live = head < total_heads;
+        const int kind = head < nq ? 0 : (head < nq + nkv ? 1 : 2);          // query, key, value
+        T* dst = row + (size_t)head * D + 4 * li;
+        if (kind != 0) {
+            const int kvh = kind == 1 ? head - nq : head - nq - nkv;
+            dst = cache_row == nullptr ? nullptr : cache_row + ((size_t)(kind - 1) * nkv + kvh) * page_size * D + 4 * li;
+        }
+        float x[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[e] = live ? to_f32(lo[p].v[e]) : 0.f, x[4 + e] = live ? to_f32(hi[p].v[e]) : 0.f;
+        if (kind != 2) {
+            if (has_norm) {                                   // every lane takes part in the shuffles
+                float ss = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+#pragma unroll
+                for (int o = L / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float factor = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = x[e] * factor * (kind == 0 ? wq[e] : wk[e]);
+            }
+            if (has_rope) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float c = cs[2 * e], sn = cs[2 * e + 1], x1 = x[e], x2 = x[4 + e];
+                    x[e] = x1 * c - x2 * sn;
+                    x[4 + e] = x2 * c + x1 * sn;
+                }
+            }
+        }
+        if (live && dst != nullptr) {
+            Vec a, b;
+            if (kind == 2) {
+                a = lo[p], b = hi[p];
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) a.v[e] = from_f32<T>(x[e]), b.v[e] = from_f32<T>(x[4 + e]);
+            }
+            *reinterpret_cast<Vec*>(dst) = a;
+            *reinterpret_cast<Vec*>(dst + D / 2) = b;
+        }
+    }
+}
+
+constexpr int kBulkTokens = 256;       // the many-token kernel from this many tokens on
+
+template <typename T>
+static cudaError_t launch_fast(int E, dim3 grid, cudaStream_t stream, bool use_pdl, T* qkv, int row_stride, const int* positions,
+                               const int* slot_mapping, AnyVec qw, AnyVec kw, int has_norm, float eps, const float* rope_table,
+                               int has_rope, int max_positions, T* cache, int num_pages, int page_size, int nq, int nkv,
+                               int write_cache, int num_tokens) {
+    if (num_tokens >= kBulkTokens && E * 32 >= 64) {
+        const int L = E * 4;                                  // lanes per head: d / 8
+        const int total_heads = write_cache ? nq + 2 * nkv : nq;
+        const int per_warp = (32 / L) * kBulkPasses;
+        const long long warps = (long long)num_tokens * ((total_heads + per_warp - 1) / per_warp);
+        dim3 bulk((unsigned)((warps + kBulkWarps - 1) / kBulkWarps));
+#define CIB_ROPE_BULK(LV)                                                                                                      \
+    if (L == LV)                                                                                                               \
+        return launch_pdl(qk_norm_rope_kv_write_bulk_kernel<T, LV>, bulk, dim3(kBulkWarps * 32), 0, stream, use_pdl, qkv,     \
+                          row_stride, positions, slot_mapping, qw, kw, has_norm, eps, rope_table, has_rope, max_positions,    \
+                          cache, num_pages, page_size, nq, nkv, write_cache, num_tokens);
+        CIB_ROPE_BULK(8)
+        CIB_ROPE_BULK(16)
+        CIB_ROPE_BULK(32)
+#undef CIB_ROPE_BULK
+    }
+#define CIB_ROPE_FAST(EV)                                                                                                   \
+    if (E == EV)                                                                                                            \
+        return launch_pdl(qk_norm_rope_kv_write_fast_kernel<T, EV>, grid, dim3(kRopeWarps * 32), 0, stream, use_pdl, qkv,   \
+                          row_stride, positions, slot_mapping, qw, kw, has_norm, eps, rope_table, has_rope, max_positions, \
+                          cache, num_pages, page_size, nq, nkv, write_cache);
+    CIB_ROPE_FAST(1)
+    CIB_ROPE_FAST(2)
+    CIB_ROPE_FAST(4)
+    CIB_ROPE_FAST(8)
+#undef CIB_ROPE_FAST
+    return cudaErrorInvalidValue;
+}
+
 }  // namespace cib
 
 using namespace cib;
@@ -109,7 +348,19 @@ extern "C" int cib_qk_norm_rope_kv_write(void* qkv, int dtype, int row_stride, c
     const size_t smem = (size_t)kRopeWarps * d * sizeof(float);
     AnyVec qw{q_weight, weight_dtype == kBF16}, kw{k_weight, weight_dtype == kBF16};
     cudaError_t e;
-    if (dtype == kF32) {
+    const int per_lane = d / 32;
+    const bool fast = d % 32 == 0 && (per_lane == 1 || per_lane == 2 || per_lane == 4 || per_lane == 8) &&
+                      (rotary_dim == 0 || rotary_dim == d) && (size_t)qkv % 16 == 0 && (size_t)cache % 16 == 0 && (size_t)rope_table % 16 == 0 &&
+                      ((size_t)row_stride * (dtype == kF32 ? 4 : 2)) % 16 == 0;
+    if (fast && dtype == kF32) {
+        e = launch_fast<float>(per_lane, grid, stream, use_pdl != 0, (float*)qkv, row_stride, positions, slot_mapping, qw, kw,
+                               has_norm, eps, rope_table, rotary_dim > 0, max_positions, (float*)cache, num_pages, page_size, nq,
+                               nkv, write_cache, num_tokens);
+    } else if (fast && dtype == kBF16) {
+        e = launch_fast<__nv_bfloat16>(per_lane, grid, stream, use_pdl != 0, (__nv_bfloat16*)qkv, row_stride, positions,
+                                       slot_mapping, qw, kw, has_norm, eps, rope_table, rotary_dim > 0, max_positions,
+                                       (__nv_bfloat16*)cache, num_pages, page_size, nq, nkv, write_cache, num_tokens);
+    } else if (dtype == kF32) {
         e = launch_pdl(qk_norm_rope_kv_write_kernel<float>, grid, dim3(kRopeWarps * 32), smem, stream, use_pdl != 0,
                        (float*)qkv, row_stride, positions, slot_mapping, qw, kw, has_norm, eps, rope_table, rotary_dim,
                        max_positions, (float*)cache, num_pages, page_size, nq, nkv, d, write_cache);

@@ -511,8 +511,8 @@ def attention_tcgen05_supports(head_dim: int, num_q_heads: int, num_kv_heads: in
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       query_start_loc: torch.Tensor, seq_lens: torch.Tensor, query_lens_host, num_q_heads: int,
                       num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
-    """bfloat16 attention for prompt portions on tcgen05 tensor cores (head size 128): scores and output
-    accumulate in tensor memory, keys and values come page by page through a 5-D TMA tensor map."""
+    """bfloat16 attention for prompt portions on tcgen05 tensor cores (head size 128, pages of 8, 16, 32, ...
+    slots): scores and output accumulate in tensor memory, keys and values come page by page through TMA."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_tcgen05: bfloat16 only")

@@ -202,12 +202,14 @@ def test_gemm_skinny_refuses_other_shapes():
 
 # ---- q/k norm + rotary + cache write ------------------------------------------------------------------------
 
-def paged_cache(k_dense, v_dense, page_size, num_pages, seed, dtype):
+def paged_cache(k_dense, v_dense, page_size, num_pages, seed, dtype, poison=False):
     """Scatter per-request dense [n, nkv, d] keys/values into shuffled pages.
     Returns (cache [pages, 2, nkv, ps, d], tables list, slot list per request)."""
     g = torch.Generator().manual_seed(seed)
     nkv, d = k_dense[0].shape[1:]
     cache = (torch.randn(num_pages, 2, nkv, page_size, d, generator=g) * 50).to(dtype)   # stale garbage everywhere
+    if poison:
+        cache.fill_(float("nan"))         # slots that hold no token of a request must never reach a result
     order = torch.randperm(num_pages, generator=g).tolist()
     tables = []
     for kd, vd in zip(k_dense, v_dense):
@@ -270,9 +272,42 @@ def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, rot):
     close(dev2[:, :nq * d], q2.reshape(T, -1), TOL[dtype])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq, nkv, d, rot", [(16, 8, 128, 128), (5, 1, 64, 64), (3, 3, 256, 0), (6, 2, 96, 96), (7, 7, 256, 256)])
+def test_qk_norm_rope_kv_write_many_tokens(dtype, nq, nkv, d, rot):
+    """From a few hundred tokens on another kernel takes several heads per warp (for head sizes 64, 128, 256): it must
+    give what the same call gives when it is cut into small pieces, which the test above checks against the plain
+    formulas (the sums of squares are added in another order, so the last bit may differ)."""
+    k = _k()
+    T, ps = 700, 16
+    pages = (T + ps - 1) // ps + 2
+    qkv = rand(T, (nq + 2 * nkv) * d, seed=14, dtype=dtype).to(DEV)
+    g = torch.Generator().manual_seed(15)
+    positions = torch.randint(0, 900, (T,), generator=g, dtype=torch.int32).to(DEV)
+    slots = torch.randperm(pages * ps, generator=g)[:T].to(torch.int32)
+    slots[::37] = -1
+    slots = slots.to(DEV)
+    qw, kw = (1 + rand(d, seed=16, scale=0.3)).to(DEV), (1 + rand(d, seed=17, scale=0.3)).to(DEV)
+    table = None
+    if rot:
+        inv = 1.0 / torch.pow(torch.tensor(10000.0), torch.arange(rot // 2, dtype=torch.float32) * 2.0 / rot)
+        ang = torch.arange(900, dtype=torch.float32)[:, None] * inv[None, :]
+        table = torch.stack((torch.cos(ang), torch.sin(ang)), -1).contiguous().to(DEV)
+    whole, cache_w = qkv.clone(), torch.full((pages, 2, nkv, ps, d), 7.0, dtype=dtype, device=DEV)
+    k.qk_norm_rope_kv_write(whole, positions, slots, qw, kw, 1e-6, table, rot, cache_w, nq, nkv, d)
+    pieces, cache_p = qkv.clone(), torch.full((pages, 2, nkv, ps, d), 7.0, dtype=dtype, device=DEV)
+    for a in range(0, T, 100):
+        k.qk_norm_rope_kv_write(pieces[a:a + 100], positions[a:a + 100], slots[a:a + 100], qw, kw, 1e-6, table, rot,
+                                cache_p, nq, nkv, d)
+    close(whole, pieces.float().cpu(), TOL[dtype])
+    close(cache_w, cache_p.float().cpu(), TOL[dtype])
+    assert torch.equal(whole[:, nq * d:].cpu(), qkv[:, nq * d:].cpu())               # k and v columns are left alone
+    assert not torch.equal(whole.cpu(), qkv.cpu())
+
+
 # ---- attention --------------------------------------------------------------------------------------------------
 
-def attention_case(dtype, nq, nkv, d, lens, new, page_size, seed, sharp=False):
+def attention_case(dtype, nq, nkv, d, lens, new, page_size, seed, sharp=False, poison=False):
     """Requests with ``lens`` tokens in the cache, the last ``new`` of them being this step's queries."""
     g = torch.Generator().manual_seed(seed)
     ks, vs, qs = [], [], []
@@ -287,7 +322,7 @@ def attention_case(dtype, nq, nkv, d, lens, new, page_size, seed, sharp=False):
                 kd[far, a // (nq // nkv)] = qd[-1, a] / qd[-1, a].norm() * 6.0 * math.sqrt(d) / (nq // nkv + 1) * (a % (nq // nkv) + 1)
         ks.append(kd.to(dtype).float()); vs.append(vd.to(dtype).float()); qs.append(qd.to(dtype).float())
     pages = sum((n + page_size - 1) // page_size for n in lens) + 3
-    cache, tables = paged_cache(ks, vs, page_size, pages, seed + 1, dtype)
+    cache, tables = paged_cache(ks, vs, page_size, pages, seed + 1, dtype, poison)
     stride = max(len(t) for t in tables) + 2
     bt = torch.full((len(lens), stride), -1, dtype=torch.int32)
     for r, t in enumerate(tables):
@@ -412,16 +447,17 @@ def test_paged_attention_decode_fused_equals_the_two_kernels(nq, nkv, d, ps, rot
     assert torch.equal(cache_b.cpu(), cache_a.cpu())
 
 
-@pytest.mark.parametrize("nq, nkv, ps", [(16, 8, 16), (8, 1, 32), (4, 4, 5), (32, 2, 128)])
+@pytest.mark.parametrize("nq, nkv, ps", [(16, 8, 16), (8, 1, 32), (4, 4, 8), (32, 2, 128), (2, 1, 256)])
 @pytest.mark.parametrize("window", [None, 200])
 def test_attention_tcgen05(nq, nkv, ps, window):
-    """The tensor-memory attention kernel on portions of every length beside decoded tokens."""
+    """The tensor-memory attention kernel on portions of every length beside decoded tokens; cache slots that hold no
+    token are NaN."""
     k = _k()
     d = 128
     assert k.attention_tcgen05_supports(d, nq, nkv, ps)
     lens = [1, 37, 64, 130, 5, 300, 257, 1000, 128, 640]
     new = [1, 37, 1, 17, 2, 300, 129, 1, 128, 513]
-    case = attention_case(torch.bfloat16, nq, nkv, d, lens, new, ps, seed=80, sharp=True)
+    case = attention_case(torch.bfloat16, nq, nkv, d, lens, new, ps, seed=80, sharp=True, poison=True)
     scale = 1.0 / math.sqrt(d)
     T = sum(new)
     out = torch.full((T, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
@@ -432,6 +468,7 @@ def test_attention_tcgen05(nq, nkv, ps, window):
         k.check_error_flags()
     close(out, attention_reference(case, lens, new, scale, window), 1.5e-2)
     assert not k.attention_tcgen05_supports(64, 8, 8, 16) and not k.attention_tcgen05_supports(128, 12, 4, 16)
+    assert not k.attention_tcgen05_supports(128, 8, 8, 5) and not k.attention_tcgen05_supports(128, 8, 8, 4)
 
 
 def test_paged_attention_decode_refuses_other_sizes():
