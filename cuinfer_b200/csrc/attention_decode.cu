@@ -12,7 +12,15 @@
 //
 // Scratch layout (float32): part_o[(request * nkv + kvh) * splits + split][g][D], part_ml[...][g][2].
 // Cache layout of one layer: [page][0 = keys, 1 = values][kv head][slot in page][D].
+//
+// Where pages hold a multiple of 16 slots and the head size is a multiple of 64 (and there is no window), the
+// blocks come through TMA instead of cp.async: one `cp.async.bulk.tensor.2d` per 64-column panel of a block's keys
+// and of its values (128-byte swizzle), counted in bytes on an mbarrier per ring stage.  An SM keeps more bytes in
+// flight this way than its load/store unit allows for cp.async, which is what bounds a kernel that only streams.
 #include "mma_utils.cuh"
+
+#include <cuda.h>
+#include <string.h>
 
 namespace cib {
 
@@ -27,6 +35,41 @@ struct DecodeSmem {
     static constexpr int kWarpBytes = kDecStages * 2 * kBlockBytes;
     static constexpr int kTotal = kDecWarps * kWarpBytes;
 };
+
+// Element offset of 16-byte chunk `chunk` of row `row` inside a 16-row block.  cp.async path: rows of D elements,
+// chunks XOR-swizzled by the row.  TMA path: 64-column panels of 16 rows x 128 bytes, chunks swizzled inside a panel.
+template <int D, bool TMA>
+__device__ __forceinline__ int block_off(int row, int chunk) {
+    if (TMA) return (chunk >> 3) * (kDecKeys * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) * 8);
+    return row * D + ((chunk ^ (row & 7)) * 8);
+}
+
+constexpr long long kDecWaitCycles = 400000000ll;     // about 0.2 s: a copy that has not landed by then never will
+
+__device__ __forceinline__ void dec_bar_init(uint64_t* b, uint32_t n) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(n));
+}
+__device__ __forceinline__ void dec_bar_expect(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool dec_bar_try(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool dec_bar_wait(uint64_t* b, uint32_t parity) {
+    if (dec_bar_try(b, parity)) return true;
+    const long long t0 = clock64();
+    while (clock64() - t0 < kDecWaitCycles)
+        if (dec_bar_try(b, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void dec_tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
 
 template <int D>
 __device__ __forceinline__ void load_block(__nv_bfloat16* sK, __nv_bfloat16* sV, const __nv_bfloat16* cache,
@@ -165,15 +208,21 @@ __device__ __forceinline__ void norm_rope_head_fast(const __nv_bfloat16* src, co
     }
 }
 
-template <int D, bool FUSED>
+template <int D, bool FUSED, bool TMA>
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                               int out_stride, const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
                               const int* __restrict__ block_table, int table_stride,
                               const int* __restrict__ seq_lens, int nq, int nkv, float scale_log2, int window,
                               int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                              int* __restrict__ counters, const DecodeFuse f) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
+                              int* __restrict__ counters, const DecodeFuse f, const __grid_constant__ CUtensorMap kv_map,
+                              int* __restrict__ error_flag) {
+    static_assert(!(FUSED && TMA), "the folded-in step writes rows of the cp.async layout");
+    extern __shared__ __align__(128) unsigned char smem_unaligned[];
+    // TMA writes whole 1024-byte swizzle atoms: the rings then start on such a boundary
+    unsigned char* smem_raw = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023))
+                                  : smem_unaligned;
+    __shared__ uint64_t s_full[kDecWarps * kDecStages];          // TMA: bytes of a ring stage have landed
     constexpr bool fused = FUSED;
     // behind the rings: finished queries [16][D], this step's key and value [2][D], a 32-bit row per warp
     __nv_bfloat16* s_q = reinterpret_cast<__nv_bfloat16*>(smem_raw + DecodeSmem<D>::kTotal);
@@ -208,6 +257,35 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int my_blocks = total_blocks > warp ? (total_blocks - warp + kDecWarps - 1) / kDecWarps : 0;
     auto block_key = [&](int i) { return k_begin + (i * kDecWarps + warp) * kDecKeys; };
 
+    if (TMA) {
+        if (threadIdx.x == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
+            for (int i = 0; i < kDecWarps * kDecStages; ++i) dec_bar_init(&s_full[i], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncthreads();
+    }
+    // TMA path: lane 0 asks for the four boxes of a block (keys and values, two 64-column panels each for D = 128);
+    // a block is 16 slots of one page (pages hold a multiple of 16 slots, blocks start at multiples of 16).  A page
+    // number outside the pool becomes a row outside the tensor map: zeros, with the bytes still counted.
+    auto tma_block = [&](int s, int key0) {
+        if (lane != 0) return;
+        const int pidx = key0 / page_size, off = key0 - pidx * page_size;
+        const int page = table[pidx];
+        const long long total_rows = (long long)num_pages * 2 * nkv * page_size;
+        const bool okp = page >= 0 && page < num_pages;
+        const long long row_k = okp ? (((long long)page * 2) * nkv + kvh) * page_size + off : total_rows;
+        const long long row_v = okp ? row_k + (long long)nkv * page_size : total_rows;
+        uint64_t* bar = &s_full[warp * kDecStages + s];
+        dec_bar_expect(bar, 2 * DecodeSmem<D>::kBlockBytes);
+#pragma unroll
+        for (int pn = 0; pn < D / 64; ++pn) {
+            dec_tma_load_2d(stage_k(s) + pn * kDecKeys * 64, &kv_map, bar, pn * 64, (int)row_k);
+            dec_tma_load_2d(stage_v(s) + pn * kDecKeys * 64, &kv_map, bar, pn * 64, (int)row_v);
+        }
+    };
+
     // Keys and values of earlier steps do not depend on the kernel before this one: their first blocks are
     // requested before `griddepcontrol.wait`.  Only the block that holds this step's own token (position
     // seq_len - 1, written by the kernel before) has to wait; so do the queries.
@@ -217,17 +295,22 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int s = 0; s < kDecStages - 1; ++s) {
         if (s < my_blocks) {
             if (!fused && block_key(s) + kDecKeys > pos) deferred = s;
+            else if (TMA) tma_block(s, block_key(s));
             else load_block<D>(stage_k(s), stage_v(s), cache, table, block_key(s), k_end, page_size, num_pages, nkv, kvh, lane);
         }
-        cp_async_commit();
+        if (!TMA) cp_async_commit();
     }
     griddep_wait();
     if (deferred >= 0) {
-        // one warp per (request, kv head): its late block is its own commit group, so let everything land first
-        // and the loop's group counting starts clean
-        load_block<D>(stage_k(deferred), stage_v(deferred), cache, table, block_key(deferred), k_end, page_size, num_pages, nkv, kvh, lane);
-        cp_async_commit();
-        cp_async_wait<0>();
+        if (TMA) {
+            tma_block(deferred, block_key(deferred));
+        } else {
+            // one warp per (request, kv head): its late block is its own commit group, so let everything land first
+            // and the loop's group counting starts clean
+            load_block<D>(stage_k(deferred), stage_v(deferred), cache, table, block_key(deferred), k_end, page_size, num_pages, nkv, kvh, lane);
+            cp_async_commit();
+            cp_async_wait<0>();
+        }
     }
     // ---- query fragments: rows 0..g-1 are the heads of this kv head, the rest are zero ----
     uint32_t qf[D / 16][4];
@@ -292,10 +375,23 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
     }
 
+    bool landed = true;
     for (int i = 0; i < my_blocks; ++i) {
-        cp_async_wait<kDecStages - 2>();
-        __syncwarp();
-        {
+        if (TMA) {
+            landed = dec_bar_wait(&s_full[warp * kDecStages + i % kDecStages], (uint32_t)((i / kDecStages) & 1));
+            landed = __all_sync(0xffffffffu, landed);
+            if (!landed) {
+                if (lane == 0) atomicExch(error_flag, 21);
+                break;
+            }
+            // the stage that block i - 1 was read from is refilled: every lane has finished reading it
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            const int nxt = i + kDecStages - 1;
+            if (nxt < my_blocks) tma_block(nxt % kDecStages, block_key(nxt));
+        } else {
+            cp_async_wait<kDecStages - 2>();
+            __syncwarp();
             const int nxt = i + kDecStages - 1;
             if (nxt < my_blocks)
                 load_block<D>(stage_k(nxt % kDecStages), stage_v(nxt % kDecStages), cache, table, block_key(nxt), k_end,
@@ -305,6 +401,13 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         const __nv_bfloat16* sK = stage_k(i % kDecStages);
         const __nv_bfloat16* sV = stage_v(i % kDecStages);
         const int key0 = block_key(i);
+        if (TMA && key0 + kDecKeys > seq_len) {
+            // the page came whole: value rows past the request's last token may hold anything, and 0 x NaN is NaN
+            const int valid = seq_len - key0;
+            for (int idx = valid * (D / 8) + lane; idx < kDecKeys * (D / 8); idx += 32)
+                *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(sV) + block_off<D, true>(idx / (D / 8), idx % (D / 8))) = make_uint4(0, 0, 0, 0);
+            __syncwarp();
+        }
         if (fused && pos >= key0 && pos < key0 + kDecKeys) {
             // the page row of this step's token was copied as the cache had it: put the fresh key and value there
             const int prow = pos - key0;
@@ -327,7 +430,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             for (int kt = 0; kt < D / 16; ++kt) {
                 const int chunkc = 2 * kt + (mat & 1);
                 uint32_t b[4];
-                ldmatrix_x4(b, smem_u32(sK + krow * D + ((chunkc ^ (krow & 7)) * 8)));
+                ldmatrix_x4(b, smem_u32(sK + block_off<D, TMA>(krow, chunkc)));
                 mma_bf16_16816(s[0], qf[kt], b[0], b[1]);
                 mma_bf16_16816(s[1], qf[kt], b[2], b[3]);
             }
@@ -378,7 +481,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             for (int nt = 0; nt < D / 16; ++nt) {
                 const int chunkc = 2 * nt + (mat >> 1);
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, smem_u32(sV + vrow * D + ((chunkc ^ (vrow & 7)) * 8)));
+                ldmatrix_x4_trans(b, smem_u32(sV + block_off<D, TMA>(vrow, chunkc)));
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     float* acc = o[2 * nt + t];
@@ -389,7 +492,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             }
         }
     }
-    cp_async_wait<0>();
+    if (!TMA) cp_async_wait<0>();
     __syncthreads();     // all rings are free: reuse shared memory for the merge of the warps
 
     // ---- merge the warps (only the g real rows) ----
@@ -498,23 +601,35 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                          int page_size, const int* block_table, int table_stride, const int* seq_lens,
                          int num_requests, int nq, int nkv, float scale, int window, int splits, float* part_o,
                          float* part_ml, int* counters, cudaStream_t stream, bool use_pdl = false,
-                         const DecodeFuse* fuse = nullptr) {
+                         const DecodeFuse* fuse = nullptr, int* error_flag = nullptr) {
     const int g = nq / nkv;
     DecodeFuse f;
     if (fuse) f = *fuse;
     else { f = DecodeFuse(); f.qkv = nullptr; f.q_weight = AnyVec{nullptr, 0}; f.k_weight = AnyVec{nullptr, 0}; }
+    // TMA needs whole 16-slot blocks inside a page, blocks that start at multiples of 16 (no window), 64-column
+    // panels, a place to report a wait that ran out, and row coordinates that fit 32 bits
+    const long long total_rows = (long long)num_pages * 2 * nkv * page_size;
+    const bool tma = !fuse && error_flag != nullptr && page_size % kDecKeys == 0 && window <= 0 && D % 64 == 0 &&
+                     total_rows < (1ll << 31) && ((uintptr_t)cache % 16) == 0;
+    CUtensorMap kv_map;
+    memset(&kv_map, 0, sizeof(kv_map));
+    if (tma && encode_tensor_map_bf16_2d(&kv_map, cache, (unsigned long long)total_rows, D, D, 64, kDecKeys,
+                                         "paged_attention_decode") != 0)
+        return -1;
     // rings, then the finished queries, the new key/value and one 32-bit row per warp
     // (only when the step before is folded in: the extra bytes keep the next kernel's CTAs off the SM otherwise)
-    size_t smem = DecodeSmem<D>::kTotal + (fuse ? (size_t)(16 + 2) * D * 2 + (size_t)kDecWarps * D * 4 : 0);
-    size_t merge = (size_t)(2 * kDecWarps * 16 + kDecWarps * g * D) * sizeof(float);
-    const size_t combine = (size_t)(g * splits + g) * sizeof(float);
+    size_t smem = DecodeSmem<D>::kTotal + (fuse ? (size_t)(16 + 2) * D * 2 + (size_t)kDecWarps * D * 4 : 0) + (tma ? 1024 : 0);
+    size_t merge = (size_t)(2 * kDecWarps * 16 + kDecWarps * g * D) * sizeof(float) + (tma ? 1024 : 0);
+    const size_t combine = (size_t)(g * splits + g) * sizeof(float) + (tma ? 1024 : 0);
     if (combine > merge) merge = combine;
     if (merge > smem) smem = merge;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+            e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
         if (e != cudaSuccess) {
             set_error("paged_attention_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
             return -2;
@@ -524,11 +639,12 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     CIB_REQUIRE(smem <= 225 * 1024, "paged_attention_decode: needs %zu bytes of shared memory", smem);
     dim3 grid(splits, nkv, num_requests);
     const float scale_log2 = scale * 1.4426950408889634f;
-    cudaError_t e = launch_pdl(fuse ? paged_attention_decode_kernel<D, true> : paged_attention_decode_kernel<D, false>, grid,
-                               dim3(kDecWarps * 32), smem, stream, use_pdl,
+    auto kernel = fuse ? paged_attention_decode_kernel<D, true, false>
+                       : (tma ? paged_attention_decode_kernel<D, false, true> : paged_attention_decode_kernel<D, false, false>);
+    cudaError_t e = launch_pdl(kernel, grid, dim3(kDecWarps * 32), smem, stream, use_pdl,
                                (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                                (const __nv_bfloat16*)cache, num_pages, page_size, block_table, table_stride, seq_lens, nq,
-                               nkv, scale_log2, window, splits, part_o, part_ml, counters, f);
+                               nkv, scale_log2, window, splits, part_o, part_ml, counters, f, kv_map, error_flag);
     if (e != cudaSuccess) {
         set_error("paged_attention_decode: launch failed: %s", cudaGetErrorString(e));
         return -2;
@@ -552,12 +668,13 @@ extern "C" long long cib_paged_attention_decode_scratch_floats(int num_requests,
 
 // One query token per request.  `scratch` holds cib_paged_attention_decode_scratch_floats floats (unused when
 // splits == 1); `counters` holds num_requests * nkv ints that are zero before the first call (the kernel leaves
-// them zero).
+// them zero).  `error_flag` (one zero int in device memory, or null) lets the kernel fetch the cache through TMA
+// where the geometry allows it: a copy that does not land in time sets the flag instead of hanging the kernel.
 extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* cache,
                                           int num_pages, int page_size, const int* block_table, int table_stride,
                                           const int* seq_lens, int num_requests, int nq, int nkv, int head_dim,
                                           float scale, int window, int splits, float* scratch, int* counters,
-                                          int use_pdl, cudaStream_t stream) {
+                                          int use_pdl, int* error_flag, cudaStream_t stream) {
     CIB_REQUIRE(cib_paged_attention_decode_supports(head_dim, nq, nkv),
                 "paged_attention_decode: head_dim %d with %d/%d heads is not taken by this kernel (64, 128 or 256; at most 16 query heads per kv head)",
                 head_dim, nq, nkv);
@@ -570,9 +687,9 @@ extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_requests * nq * splits * head_dim : nullptr;
     switch (head_dim) {
-        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0);
-        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0);
-        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0);
+        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag);
+        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag);
+        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag);
     }
     return -1;
 }

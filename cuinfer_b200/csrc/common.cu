@@ -47,4 +47,4 @@ int encode_tensor_map_bf16_2d(void* map, const void* base, unsigned long long ro
 extern "C" const char* cib_last_error() { return cib::g_error; }
 
 // Bumped whenever an exported signature changes, so that a stale library is rebuilt, not misused.
-extern "C" int cib_abi_version() { return 1; }
+extern "C" int cib_abi_version() { return 2; }

@@ -14,6 +14,7 @@ from typing import List, Optional, Sequence, Union
 
 from ..config import EngineConfig
 from ..sampling import SamplingParams
+from .. import kernels
 from .core import EngineCore
 from .scheduler import FinishReason
 
@@ -73,4 +74,5 @@ class LLM:
                     res = results[out.request_id]
                     res.token_ids.extend(out.new_token_ids)
                     res.finish_reason = out.finish_reason.value
+        kernels.check_error_flags(force=True)
         return [results[rid] for rid in order]

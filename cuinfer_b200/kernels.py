@@ -70,7 +70,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_silu_mul": [_P, _P, _I, _I, _I, _P],
         "cib_qk_norm_rope_kv_write": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
-        "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P],
+        "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _P],
         "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
         "cib_paged_attention_decode_fused": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I,
                                              _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P],
@@ -256,32 +256,44 @@ def paged_attention_decode_supports(head_dim: int, num_q_heads: int, num_kv_head
     return bool(library().cib_paged_attention_decode_supports(head_dim, num_q_heads, num_kv_heads))
 
 
+# CUINFER_B200_DECODE_TMA=0 keeps the decode attention kernel on its cp.async path (for comparisons).
+decode_tma = os.environ.get("CUINFER_B200_DECODE_TMA", "1") != "0"
+
+
 def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots: int = 296) -> int:
     """How many CTAs share the keys of one (request, kv head).
 
-    The GPU runs ``slots`` CTAs of this kernel at a time (two on each of the 148 SMs).  A launch's time is
-    estimated as (rounds of CTAs) x (keys per CTA + a fixed cost per CTA worth about 150 keys) + 11 key-times
-    per split for the combine; the constants were fitted to timings at batch 1, 8 and 64 with 4096 keys.
-    The number of splits with the smallest estimate wins, and a split never gets fewer than 64 keys.
+    The GPU runs ``slots`` CTAs of this kernel at a time (two on each of the 148 SMs); a CTA's four warps take
+    16-key blocks in turn, so a CTA's share counts in steps of 64 keys.  A launch is estimated, in nanoseconds, as
+    the larger of the time the memory needs for all keys and values, and (rounds of CTAs) x (keys per CTA x 19.5
+    + 4400 for a CTA's start, merge and partial results), plus 75 per split for the combine.  The constants were
+    fitted to timings at batch 1, 8 and 64 with 4096 keys of head size 128.  The smallest estimate wins.
     """
     pairs = max(1, num_requests * num_kv_heads)
     best, best_cost = 1, None
     for s in range(1, 65):
-        keys = -(-max_seq_len // s)
-        if s > 1 and keys < 64:
-            break
-        rounds = -(-pairs * s // slots)
-        cost = rounds * (keys + 150) + 11 * s
+        keys = -(-(-(-max_seq_len // s)) // 64) * 64
+        if s > 1 and (s - 1) * keys >= max_seq_len:
+            continue                                   # the last CTA would get nothing: a smaller s does the same
+        ctas = pairs * s
+        memory = ctas * keys * 0.0788
+        chain = -(-ctas // slots) * (keys * 19.5 + 4400.0)
+        cost = max(memory, chain) + (75.0 * s if s > 1 else 0.0)
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
 
 
+DECODE_TMA_MIN_KEYS = 1536      # keys per CTA from which the TMA path of the decode kernel pays (measured)
+
+
 def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                            seq_lens: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                           window: int, splits: int) -> None:
+                           window: int, splits: int, tma: bool | None = None) -> None:
     """bfloat16 attention of one query token per request (``q[r, :nq*d]``) over the paged cache, the keys of
-    every (request, kv head) split over ``splits`` CTAs.  Allocates the partial-result scratch with torch."""
+    every (request, kv head) split over ``splits`` CTAs.  Allocates the partial-result scratch with torch.
+    ``tma``: let the kernel fetch the cache through TMA where the geometry allows it (default: yes).  That path
+    streams faster but starts slower, so callers that know the keys per CTA pass False for short streams."""
     R = q.shape[0]
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("paged_attention_decode: bfloat16 only")
@@ -307,8 +319,10 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
         _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
         block_table.stride(0), _cuda(seq_lens, "seq_lens", torch.int32), R, num_q_heads, num_kv_heads, head_dim,
         float(scale), int(window), int(splits), scratch.data_ptr() if scratch is not None else None,
-        counters.data_ptr() if counters is not None else None, 1 if use_pdl else 0, _stream())
+        counters.data_ptr() if counters is not None else None, 1 if use_pdl else 0,
+        _error_flag(q.device).data_ptr() if decode_tma and tma is not False else None, _stream())
     _check(rc, "paged_attention_decode")
+    note_flagged_launch()
     _count()
 
 
@@ -488,15 +502,29 @@ def _error_flag(device: torch.device) -> torch.Tensor:
 
 
 _flagged_launches = 0
+_unchecked_steps = 0
+CHECK_EVERY = 32          # a captured step that is replayed is looked at this often, not after every replay
 
 
-def check_error_flags() -> None:
+def note_flagged_launch(replayed: bool = False) -> None:
+    """Record that a kernel with bounded waits has run.  ``replayed``: it ran as part of a replayed CUDA graph, which
+    happens every decode step; the flag is then read only every ``CHECK_EVERY`` steps (and whenever ``force`` is given),
+    so that a step does not pay a device-to-host read for it."""
+    global _flagged_launches, _unchecked_steps
+    if replayed:
+        _unchecked_steps += 1
+    else:
+        _flagged_launches += 1
+
+
+def check_error_flags(force: bool = False) -> None:
     """Raise if a kernel gave up on a bounded wait since the last check.  Reads one int per device (which
     synchronises), but only if such a kernel was launched since the last check."""
-    global _flagged_launches
-    if _flagged_launches == 0:
+    global _flagged_launches, _unchecked_steps
+    if _flagged_launches == 0 and not (_unchecked_steps >= CHECK_EVERY or (force and _unchecked_steps)):
         return
     _flagged_launches = 0
+    _unchecked_steps = 0
     for index, flag in _error_flags.items():
         code = int(flag.item())
         if code:
@@ -527,8 +555,7 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
         _cuda(seq_lens, "seq_lens", torch.int32), len(query_lens_host), tiles, num_q_heads, num_kv_heads, head_dim,
         float(scale), int(window), _error_flag(q.device).data_ptr(), _stream())
     _check(rc, "attention_tcgen05")
-    global _flagged_launches
-    _flagged_launches += 1
+    note_flagged_launch()
     _count()
 
 
@@ -549,8 +576,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         _cuda(out, "out", contiguous=False), out.stride(0), 1 if out.dtype == torch.float32 else 0, M, N, K,
         _error_flag(a.device).data_ptr(), _stream())
     _check(rc, "gemm_tcgen05")
-    global _flagged_launches
-    _flagged_launches += 1
+    note_flagged_launch()
     _count()
 
 

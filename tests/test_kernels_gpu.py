@@ -371,15 +371,18 @@ def test_paged_attention_decode(nq, nkv, d, ps, splits, window):
     assert k.paged_attention_decode_supports(d, nq, nkv)
     lens = [1, 2, 15, 16, 17, 64, 333, 1000]
     new = [1] * len(lens)
-    case = attention_case(torch.bfloat16, nq, nkv, d, lens, new, ps, seed=30, sharp=True)
+    # slots that hold no token are NaN: pages that come whole (the TMA path, pages of 16, 32, ... slots without a
+    # window) must not let them through
+    case = attention_case(torch.bfloat16, nq, nkv, d, lens, new, ps, seed=30, sharp=True, poison=True)
     scale = 1.0 / math.sqrt(d)
     out = torch.full((len(lens), nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
     sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
     cache, bt, wide = case["cache"].to(DEV), case["bt"].to(DEV), case["wide"].to(DEV)
     want = attention_reference(case, lens, new, scale, window)
-    for _ in range(2):                     # twice: the split counters must be left at zero
+    for tma in (None, False, None):        # both ways of fetching the cache; again: the split counters must be left at zero
         out.fill_(5.0)
-        k.paged_attention_decode(wide, out, cache, bt, sl, nq, nkv, d, scale, window or 0, splits)
+        k.paged_attention_decode(wide, out, cache, bt, sl, nq, nkv, d, scale, window or 0, splits, tma=tma)
+        k.check_error_flags()
         close(out, want, 1.5e-2)
     # the all-sizes kernel agrees on the same inputs
     gen = torch.empty_like(out)
