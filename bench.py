@@ -28,6 +28,17 @@ MODEL = dict(
     architectures=["Qwen3ForCausalLM"], num_hidden_layers=28, hidden_size=1024, num_attention_heads=16,
     num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=151936, rope_theta=1000000.0,
     rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096, torch_dtype="bfloat16")
+# The other shapes of BASELINE.json (configs[3], configs[4]); chosen with --shape, with --layers fewer layers.
+SHAPES = {
+    "0.6b": ("Qwen3-0.6B shape (BASELINE configs[2])", MODEL),
+    "8b": ("Qwen3-8B shape (BASELINE configs[3])", dict(
+        MODEL, num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+        intermediate_size=12288, tie_word_embeddings=False)),
+    "32b": ("Qwen3-32B shape (BASELINE configs[4])", dict(
+        MODEL, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
+        intermediate_size=25600, tie_word_embeddings=False)),
+}
+MODEL_NAME = SHAPES["0.6b"][0]
 CONTEXT = 4096
 BLOCK_SIZE = 16
 PREFILL_TOKENS = 2048
@@ -228,13 +239,18 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
+    parser.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes (default: the 0.6B shape)")
+    parser.add_argument("--layers", type=int, default=0,
                         help="fewer layers than the configuration's, if memory or time needs it (reported)")
     parser.add_argument("--disable-cuda-graph", action="store_true")
     parser.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the prefill measurement")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    global MODEL, MODEL_NAME
+    MODEL_NAME, MODEL = SHAPES[args.shape]
+    if args.layers <= 0:
+        args.layers = MODEL["num_hidden_layers"]
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -273,10 +289,10 @@ def main() -> int:
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0, 0.02) seed 0, uniform-random token ids", "impl": "ours",
         "config": {
-            "model": "Qwen3-0.6B shape (BASELINE configs[2])", "layers": args.layers,
+            "model": MODEL_NAME, "layers": args.layers,
             "layers_full": MODEL["num_hidden_layers"], "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
-            "vocab": cfg["vocab_size"], "tied_embeddings": True, "global_batch": args.batch, "seq_len": CONTEXT,
+            "vocab": cfg["vocab_size"], "tied_embeddings": bool(cfg["tie_word_embeddings"]), "global_batch": args.batch, "seq_len": CONTEXT,
             "prompt_len": main_run["prompt_len"], "kv_block_size": BLOCK_SIZE, "parallelism": "single GPU",
             "cuda_graph": not args.disable_cuda_graph, "l2": "no flush: each step reads >1 GB, far more than the 126 MB L2",
             "peaks": peaks["source"],

@@ -346,9 +346,10 @@ static int dispatch_skinny(SkinnyArgs& a, int epilogue, int use_pdl, cudaStream_
     // As few 16-row tiles per CTA as keep the launch within one round of CTAs (two fit on each of the 148 SMs);
     // the warps that are not needed for rows split K instead.
     const int tiles = (a.N + 15) / 16;
-    if (a.res_in == nullptr && tiles <= 74 && a.K >= 3072) {
+    if (a.res_in == nullptr && tiles <= 148 && a.K >= 3072) {
         // few output features and a long K: four CTAs of a cluster share each tile so that most SMs stream
-        // (a cluster launch costs about a microsecond more, so shorter K stays with one CTA per tile)
+        // (a cluster launch costs about a microsecond more, so shorter K stays with one CTA per tile; with more
+        // tiles than SMs the split measured slower)
         if (epilogue == kStoreF32) return launch_skinny<MT, 1, 8, kStoreF32, 4>(a, tiles, use_pdl, stream);
         return launch_skinny<MT, 1, 8, kStoreBf16, 4>(a, tiles, use_pdl, stream);
     }
