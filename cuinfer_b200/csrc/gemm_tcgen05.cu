@@ -119,11 +119,16 @@ __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 1
 
 // TMA_STORE: bfloat16 results leave through a 128-byte-swizzled staging buffer and `cp.async.bulk.tensor` stores
 // (whole 128-byte lines per row; tails clipped by the tensor map).  Otherwise every thread stores its row itself.
-template <int BN, int STAGES, bool F32OUT, bool TMA_STORE>
+// SILU: the weight rows are (gate, up) halves, rows [0, up_offset) and [up_offset, 2 up_offset); a tile multiplies BN / 2
+// gate rows and the matching BN / 2 up rows (two weight boxes per stage) and stores silu(gate) * up, BN / 2 columns wide,
+// straight from the 32-bit accumulators: the activation kernel and the round trip of the gate/up matrix are gone.
+template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, bool SILU = false>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, void* __restrict__ out, int ldo, int M, int N, int K,
-                    int* __restrict__ error_flag) {
+                    int up_offset, int* __restrict__ error_flag) {
+    static_assert(!SILU || (BN == 256 && TMA_STORE && !F32OUT), "the gated epilogue is built for 256-wide tiles stored by TMA");
+    constexpr int kOutCols = SILU ? BN / 2 : BN;      // output columns of a tile
     extern __shared__ unsigned char smem_raw[];
     // stages must start on a 1024-byte boundary (one swizzle atom)
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -138,7 +143,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_steps = (K + kTcBK - 1) / kTcBK;
-    const int n_blocks = (N + BN - 1) / BN, m_blocks = (M + kTcBM - 1) / kTcBM;
+    const int n_out = SILU ? up_offset : N;
+    const int n_blocks = (n_out + kOutCols - 1) / kOutCols, m_blocks = (M + kTcBM - 1) / kTcBM;
     const int num_tiles = n_blocks * m_blocks;
 
     if (threadIdx.x == 0) {
@@ -163,7 +169,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int step = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / n_blocks) * kTcBM, n0 = (tile % n_blocks) * BN;
+                const int m0 = (tile / n_blocks) * kTcBM, n0 = (tile % n_blocks) * kOutCols;
                 for (int kb = 0; kb < k_steps; ++kb, ++step) {
                     const int s = step % STAGES;
                     const uint32_t phase = (step / STAGES) & 1;
@@ -173,7 +179,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     unsigned char* b_dst = a_dst + TcSmem<BN, STAGES>::kABytes;
                     mbar_expect_tx(&full[s], TcSmem<BN, STAGES>::kStageBytes);
                     tma_load_2d(a_dst, &map_a, &full[s], kb * kTcBK, m0);
-                    tma_load_2d(b_dst, &map_w, &full[s], kb * kTcBK, n0);
+                    if (SILU) {
+                        // gate rows, then the matching up rows: accumulator columns [0, BN/2) and [BN/2, BN)
+                        tma_load_2d(b_dst, &map_w, &full[s], kb * kTcBK, n0);
+                        tma_load_2d(b_dst + (BN / 2) * 128, &map_w, &full[s], kb * kTcBK, up_offset + n0);
+                    } else {
+                        tma_load_2d(b_dst, &map_w, &full[s], kb * kTcBK, n0);
+                    }
                 }
             }
         }
@@ -216,14 +228,60 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
-            const int m0 = (tile / n_blocks) * kTcBM, n0 = (tile % n_blocks) * BN;
+            const int m0 = (tile / n_blocks) * kTcBM, n0 = (tile % n_blocks) * kOutCols;
             const int row = m0 + quarter * 32 + lane;
             ok = mbar_wait(&acc_full[buf], acc_phase);
             if (!ok && lane == 0) { atomicExch(error_flag, 3); s_abort = 1; }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
             if (!ok) break;
             tcgen05_fence_after();
-            if (TMA_STORE) {
+            if constexpr (SILU) {
+                const int r_local = quarter * 32 + lane;
+                const bool store_thread = threadIdx.x == 64;
+                if (store_thread) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging is free again
+                epilogue_barrier();
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t gv[32], uv[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c * 32);
+                    tmem_ld_32x32b_x32(taddr, gv);
+                    tmem_ld_32x32b_x32(taddr + (uint32_t)(BN / 2), uv);
+                    tmem_ld_wait();
+                    if (c == 3) {
+                        tcgen05_fence_before();
+                        if (lane == 0) mbar_arrive(&acc_empty[buf]);     // the accumulator has been read completely
+                    }
+                    unsigned char* panel = staging + (size_t)(c >> 1) * (kTcBM * 128) + (size_t)r_local * 128;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float y[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float g = __uint_as_float(gv[8 * j + e]), u = __uint_as_float(uv[8 * j + e]);
+                            // the hardware's exponential and reciprocal (2 ulp): far below the bfloat16 rounding of
+                            // the result, and the exact ones would make the epilogue longer than the tile's MMAs
+                            y[e] = __fdividef(g, 1.f + __expf(-g)) * u;
+                        }
+                        uint4 pk;
+                        __nv_bfloat162 t0 = __floats2bfloat162_rn(y[0], y[1]), t1 = __floats2bfloat162_rn(y[2], y[3]);
+                        __nv_bfloat162 t2 = __floats2bfloat162_rn(y[4], y[5]), t3 = __floats2bfloat162_rn(y[6], y[7]);
+                        pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
+                        pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
+                        const int chunk = ((c & 1) * 4 + j) ^ (r_local & 7);       // 128-byte swizzle
+                        *reinterpret_cast<uint4*>(panel + chunk * 16) = pk;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                epilogue_barrier();
+                if (store_thread) {
+#pragma unroll
+                    for (int p = 0; p < 2; ++p) {
+                        const int col = n0 + p * 64;
+                        if (col < n_out) tma_store_2d(&map_out, staging + (size_t)p * (kTcBM * 128), col, m0);
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+            } else if constexpr (TMA_STORE) {
                 const int r_local = quarter * 32 + lane;                 // row of the tile = TMEM lane
                 const bool store_thread = threadIdx.x == 64;
 #pragma unroll 1
@@ -265,8 +323,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 }
-                continue;
-            }
+            } else {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
@@ -313,6 +370,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             }
+            }
         }
     }
     // ---- teardown: everything issued has been waited for on the normal path; free the tensor memory ----
@@ -354,10 +412,10 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
     return 0;
 }
 
-template <int BN, int STAGES, bool F32OUT, bool TMA_STORE>
+template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, bool SILU = false>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, void* out, int ldo, int M, int N,
-                     int K, int* error_flag, cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_kernel<BN, STAGES, F32OUT, TMA_STORE>;
+                     int K, int* error_flag, cudaStream_t stream, int up_offset = 0) {
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, F32OUT, TMA_STORE, SILU>;
     constexpr int smem = TcSmem<BN, STAGES>::kTotal;
     static bool configured = false;
     if (!configured) {
@@ -374,9 +432,10 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtenso
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
     }
-    const int tiles = ((N + BN - 1) / BN) * ((M + kTcBM - 1) / kTcBM);
+    const int out_cols = SILU ? BN / 2 : BN, n_out = SILU ? up_offset : N;
+    const int tiles = ((n_out + out_cols - 1) / out_cols) * ((M + kTcBM - 1) / kTcBM);
     dim3 grid(tiles < num_sms ? tiles : num_sms);
-    kernel<<<grid, 192, smem, stream>>>(ma, mw, mo, out, ldo, M, N, K, error_flag);
+    kernel<<<grid, 192, smem, stream>>>(ma, mw, mo, out, ldo, M, N, K, up_offset, error_flag);
     CIB_LAUNCH_CHECK("gemm_tcgen05");
     return 0;
 }
@@ -391,13 +450,24 @@ extern "C" int cib_gemm_tcgen05_supports(int M, int N, int K) {
 
 // a: [M, K] bfloat16 rows (lda), w: [N, K] bfloat16 rows (ldw), out: [M, N] bfloat16 (out_f32 = 0) or float32.
 // error_flag: one int in device memory, zero before the call; non-zero afterwards means a bounded wait gave up.
-extern "C" int cib_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ldo, int out_f32, int M,
-                                int N, int K, int* error_flag, cudaStream_t stream) {
+// silu_pair: w holds N / 2 gate rows followed by N / 2 up rows and out is [M, N / 2] bfloat16 = silu(a gate^T) * (a up^T).
+extern "C" int cib_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ldo, int out_f32, int silu_pair,
+                                int M, int N, int K, int* error_flag, cudaStream_t stream) {
     CIB_REQUIRE(cib_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M=%d N=%d K=%d is not taken (K must be a multiple of 8)", M, N, K);
     CIB_REQUIRE(lda >= K && ldw >= K && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: row strides must be multiples of 8 elements");
     CIB_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
-    CIB_REQUIRE(ldo >= N && error_flag != nullptr, "gemm_tcgen05: bad output arguments");
+    CIB_REQUIRE(ldo >= (silu_pair ? N / 2 : N) && error_flag != nullptr, "gemm_tcgen05: bad output arguments");
     CUtensorMap ma, mw;
+    if (silu_pair) {
+        const int half = N / 2;
+        CIB_REQUIRE(N % 2 == 0 && !out_f32 && ldo % 8 == 0 && ((uintptr_t)out % 16) == 0,
+                    "gemm_tcgen05: the gated epilogue stores bfloat16 rows that are 16-byte aligned, N even");
+        CUtensorMap mo;
+        if (make_map(&ma, a, M, K, lda, kTcBM) != 0 || make_map(&mw, w, N, K, ldw, 128) != 0 ||
+            make_map(&mo, out, M, half, ldo, kTcBM) != 0)
+            return -1;
+        return launch_tc<256, 4, false, true, true>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream, half);
+    }
     // Tile width: 256 when that still gives most SMs a tile, else 128.
     const int m_blocks = (M + 127) / 128;
     int bn = 128;

@@ -76,7 +76,7 @@ def _declare(lib: ctypes.CDLL) -> None:
                                              _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P],
         "cib_attention_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
         "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P],
-        "cib_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
+        "cib_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
         "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
     }
@@ -563,18 +563,22 @@ def gemm_tcgen05_supports(M: int, N: int, K: int) -> bool:
     return bool(library().cib_gemm_tcgen05_supports(M, N, K))
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, N] = a[M, K] @ w[N, K]^T on tcgen05 tensor cores (bfloat16 in, bfloat16 or float32 out)."""
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, silu_pair: bool = False) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T on tcgen05 tensor cores (bfloat16 in, bfloat16 or float32 out).
+    ``silu_pair``: w holds N/2 gate rows then N/2 up rows and out[M, N/2] = silu(gate) * up (bfloat16)."""
     M, K = a.shape
     N, K2 = w.shape
-    if K != K2 or out.shape != (M, N) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+    out_cols = N // 2 if silu_pair else N
+    if K != K2 or out.shape != (M, out_cols) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm_tcgen05: a {list(a.shape)} {a.dtype}, w {list(w.shape)} {w.dtype}, out {list(out.shape)} do not fit")
     if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("gemm_tcgen05: rows must be dense and out bfloat16 or float32")
+    if silu_pair and (N % 2 or out.dtype != torch.bfloat16 or out.stride(0) % 8 or out.data_ptr() % 16):
+        raise KernelError("gemm_tcgen05: the gated epilogue needs an even N and 16-byte aligned bfloat16 rows")
     rc = library().cib_gemm_tcgen05(
         _cuda(a, "a", contiguous=False), a.stride(0), _cuda(w, "w", contiguous=False), w.stride(0),
-        _cuda(out, "out", contiguous=False), out.stride(0), 1 if out.dtype == torch.float32 else 0, M, N, K,
-        _error_flag(a.device).data_ptr(), _stream())
+        _cuda(out, "out", contiguous=False), out.stride(0), 1 if out.dtype == torch.float32 else 0,
+        1 if silu_pair else 0, M, N, K, _error_flag(a.device).data_ptr(), _stream())
     _check(rc, "gemm_tcgen05")
     note_flagged_launch()
     _count()

@@ -1,7 +1,8 @@
 """Choice of the bfloat16 matrix-product kernel for a given shape.
 
 * up to 16 rows (decode steps): the few-rows kernel (``gemm_skinny``), weights streamed once;
-* 128 rows and more (prompt portions): the tcgen05 / TMA / TMEM kernel (``gemm_tcgen05``);
+* 128 rows and more (prompt portions): the tcgen05 / TMA / TMEM kernel (``gemm_tcgen05``), with the SiLU gate in its
+  epilogue for the gate/up projection;
 * in between, and for K that is not a multiple of 8: the library product (cuBLAS via ``torch.mm``; the reference
   calls cuBLAS for every projection, csrc/ops/projection.cu:32-44), or the FMA kernel for shapes cuBLAS's
   tensor-core paths do not take.
@@ -20,6 +21,24 @@ TCGEN05_MIN_ROWS = 128
 _FORCE_CUBLAS = os.environ.get("CUINFER_B200_GEMM", "") == "cublas"
 
 
+def takes_tcgen05(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    M, K = x.shape
+    return (M >= TCGEN05_MIN_ROWS and not _FORCE_CUBLAS and x.stride(1) == 1 and weight.stride(1) == 1
+            and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+            and kernels.gemm_tcgen05_supports(M, weight.shape[0], K))
+
+
+def bf16_gated_matmul_nt(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor | None:
+    """silu(x gate^T) * (x up^T) for a weight of gate rows then up rows, in one tcgen05 kernel, when the shape is one
+    it takes (prompt-sized, half of N a multiple of 8); None otherwise."""
+    N = weight.shape[0]
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or N % 16 or not takes_tcgen05(x, weight):
+        return None
+    out = torch.empty((x.shape[0], N // 2), dtype=torch.bfloat16, device=x.device)
+    kernels.gemm_tcgen05(x, weight, out, silu_pair=True)
+    return out
+
+
 def bf16_matmul_nt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, N] = x[M, K] @ weight[N, K]^T; x and weight bfloat16, out bfloat16 or float32."""
     M, K = x.shape
@@ -27,8 +46,7 @@ def bf16_matmul_nt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     if M <= 16 and weight.is_contiguous() and kernels.gemm_skinny_supports(M, N, K):
         kernels.gemm_skinny(weight, out, act=x)
         return
-    if (M >= TCGEN05_MIN_ROWS and not _FORCE_CUBLAS and x.stride(1) == 1 and weight.stride(1) == 1
-            and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and kernels.gemm_tcgen05_supports(M, N, K)):
+    if takes_tcgen05(x, weight):
         kernels.gemm_tcgen05(x, weight, out)
         return
     if K % 8 == 0 and N % 8 == 0 and x.is_contiguous() and weight.is_contiguous():

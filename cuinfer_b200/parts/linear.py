@@ -71,6 +71,11 @@ class Linear:
             return fused
         if isinstance(x, LazyNorm):
             x = x.materialize()
+        if silu_pair and x.dtype == torch.bfloat16 and x.shape[0] > 0:
+            from . import gemm_dispatch
+            gated = gemm_dispatch.bf16_gated_matmul_nt(x, self.weight)
+            if gated is not None:
+                return gated
         y = matmul_nt(x, self.weight, out_dtype if not silu_pair else None)
         if not silu_pair:
             return y

@@ -137,6 +137,26 @@ def test_gemm_tcgen05(M, N, K, f32_out):
     assert torch.equal(out2.cpu(), out.cpu())
 
 
+@pytest.mark.parametrize("M, I, K", [(128, 128, 64), (300, 3072, 1024), (2048, 200, 136), (129, 1000, 72), (513, 64, 2048)])
+def test_gemm_tcgen05_gated(M, I, K):
+    """Gate rows and up rows in one tile, silu(gate) * up from the 32-bit accumulators: widths that end inside a
+    tile, and rows that end inside one."""
+    k = _k()
+    a = rand(M, K, seed=23, dtype=torch.bfloat16)
+    w = rand(2 * I, K, seed=24, scale=0.08, dtype=torch.bfloat16)
+    out = torch.full((M, I), 7.0, dtype=torch.bfloat16, device=DEV)
+    k.gemm_tcgen05(a.to(DEV), w.to(DEV), out, silu_pair=True)
+    k.check_error_flags()
+    y = a.double() @ w.double().T
+    want = torch.nn.functional.silu(y[:, :I]) * y[:, I:]
+    close(out, want, 6e-3)
+    # as part of a wider buffer, the columns beside it stay as they were
+    wide = torch.full((M, I + 24), 7.0, dtype=torch.bfloat16, device=DEV)
+    k.gemm_tcgen05(a.to(DEV), w.to(DEV), wide[:, :I], silu_pair=True)
+    k.check_error_flags()
+    assert torch.equal(wide[:, :I].cpu(), out.cpu()) and bool((wide[:, I:] == 7.0).all())
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N, K", [(1024, 1024), (48, 96), (1000, 2048), (3000, 72), (151936, 1024)])
 def test_gemm_skinny(M, N, K):
