@@ -19,6 +19,7 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <stdlib.h>
 
 namespace cib {
 
@@ -98,10 +99,49 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-template <int BN, int STAGES>
+// ---- two CTAs on one tile (cta_group::2): the pair multiplies 256 rows x BN columns; each CTA holds its 128 rows of
+// the activations and half of the weight rows, the first CTA of the pair issues the MMAs for both, and both
+// accumulate their 128 rows in their own tensor memory ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `p` (an address in this CTA's shared memory) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(tc_smem_u32(p)), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// the copy lands in this CTA's shared memory, its bytes are counted on a barrier of the pair's first CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair when the MMAs issued so far have finished
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(tc_smem_u32(bar)), "h"(mask) : "memory");
+}
+
+template <int BN, int STAGES, bool PAIR = false>
 struct TcSmem {
     static constexpr int kABytes = kTcBM * kTcBK * 2;
-    static constexpr int kBBytes = BN * kTcBK * 2;
+    static constexpr int kBBytes = (PAIR ? BN / 2 : BN) * kTcBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStagingBytes = kTcBM * 128 * 2;        // 128 rows x 128 bfloat16 columns for the TMA store
     static constexpr int kTotal = STAGES * kStageBytes + kStagingBytes + 1024 /* alignment slack */ + 512 /* barriers */;
@@ -122,7 +162,10 @@ __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 1
 // SILU: the weight rows are (gate, up) halves, rows [0, up_offset) and [up_offset, 2 up_offset); a tile multiplies BN / 2
 // gate rows and the matching BN / 2 up rows (two weight boxes per stage) and stores silu(gate) * up, BN / 2 columns wide,
 // straight from the 32-bit accumulators: the activation kernel and the round trip of the gate/up matrix are gone.
-template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, bool SILU = false>
+// PAIR: launched as clusters of two CTAs that share each 256 x BN tile (see the helpers above).  Per 64-k step a CTA
+// then fetches 16 KB of activations and BN / 2 weight rows instead of BN: the kernel is bound by what an SM can fetch
+// from the L2, so fewer bytes per flop is what makes it faster.
+template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, bool SILU = false, bool PAIR = false>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, void* __restrict__ out, int ldo, int M, int N, int K,
@@ -132,8 +175,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     extern __shared__ unsigned char smem_raw[];
     // stages must start on a 1024-byte boundary (one swizzle atom)
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* staging = tiles + STAGES * TcSmem<BN, STAGES>::kStageBytes;      // 1024-byte aligned as well
-    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + TcSmem<BN, STAGES>::kStagingBytes);
+    unsigned char* staging = tiles + STAGES * TcSmem<BN, STAGES, PAIR>::kStageBytes;      // 1024-byte aligned as well
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + TcSmem<BN, STAGES, PAIR>::kStagingBytes);
     uint64_t* full = bars;                     // [STAGES]  bytes of a stage have landed
     uint64_t* empty = bars + STAGES;           // [STAGES]  the MMAs that read a stage are done
     uint64_t* acc_full = bars + 2 * STAGES;    // [2]       an accumulator holds a finished tile
@@ -143,23 +186,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_steps = (K + kTcBK - 1) / kTcBK;
+    constexpr int kTileRows = PAIR ? 2 * kTcBM : kTcBM;       // rows of a tile (of the pair's tile)
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;       // 0: the CTA that issues the MMAs
+    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const int n_out = SILU ? up_offset : N;
-    const int n_blocks = (n_out + kOutCols - 1) / kOutCols, m_blocks = (M + kTcBM - 1) / kTcBM;
+    const int n_blocks = (n_out + kOutCols - 1) / kOutCols, m_blocks = (M + kTileRows - 1) / kTileRows;
     const int num_tiles = n_blocks * m_blocks;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], PAIR ? 8 : 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();          // the other CTA's barriers exist before anything arrives on them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -168,16 +221,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // ---- TMA producer: one running step counter over all tiles of this CTA ----
             int step = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / n_blocks) * kTcBM, n0 = (tile % n_blocks) * kOutCols;
+            for (int tile = worker; tile < num_tiles && ok; tile += workers) {
+                const int m0 = (tile / n_blocks) * kTileRows + (int)rank * kTcBM, n0 = (tile % n_blocks) * kOutCols;
                 for (int kb = 0; kb < k_steps; ++kb, ++step) {
                     const int s = step % STAGES;
                     const uint32_t phase = (step / STAGES) & 1;
                     if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 1); s_abort = 1; ok = false; break; }
                     if (*(volatile int*)&s_abort) { ok = false; break; }
-                    unsigned char* a_dst = tiles + (size_t)s * TcSmem<BN, STAGES>::kStageBytes;
-                    unsigned char* b_dst = a_dst + TcSmem<BN, STAGES>::kABytes;
-                    mbar_expect_tx(&full[s], TcSmem<BN, STAGES>::kStageBytes);
+                    unsigned char* a_dst = tiles + (size_t)s * TcSmem<BN, STAGES, PAIR>::kStageBytes;
+                    unsigned char* b_dst = a_dst + TcSmem<BN, STAGES, PAIR>::kABytes;
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes are counted on the first CTA's barrier; it expects them all
+                        const uint32_t bar = map_to_cta(&full[s], 0);
+                        if (rank == 0) mbar_expect_tx(&full[s], 2 * TcSmem<BN, STAGES, PAIR>::kStageBytes);
+                        tma_load_2d_pair(a_dst, &map_a, bar, kb * kTcBK, m0);
+                        // this CTA's half of the tile's weight rows (gated: the first CTA the gates, the second the ups)
+                        const int w_row = SILU ? (rank == 0 ? n0 : up_offset + n0) : n0 + (int)rank * (BN / 2);
+                        tma_load_2d_pair(b_dst, &map_w, bar, kb * kTcBK, w_row);
+                        continue;
+                    }
+                    mbar_expect_tx(&full[s], TcSmem<BN, STAGES, PAIR>::kStageBytes);
                     tma_load_2d(a_dst, &map_a, &full[s], kb * kTcBK, m0);
                     if (SILU) {
                         // gate rows, then the matching up rows: accumulator columns [0, BN/2) and [BN/2, BN)
@@ -190,12 +253,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- MMA issuer ----
-            constexpr uint32_t idesc = umma_idesc_bf16(kTcBM, BN);
+        if (lane == 0 && rank == 0) {
+            // ---- MMA issuer (of the pair) ----
+            constexpr uint32_t idesc = umma_idesc_bf16(kTileRows, BN);
             int step = 0, local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            for (int tile = worker; tile < num_tiles && ok; tile += workers, ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
                 if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1)) { atomicExch(error_flag, 4); s_abort = 1; ok = false; break; }
@@ -206,18 +269,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t phase = (step / STAGES) & 1;
                     if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 2); s_abort = 1; ok = false; break; }
                     tcgen05_fence_after();
-                    const unsigned char* a_src = tiles + (size_t)s * TcSmem<BN, STAGES>::kStageBytes;
-                    const unsigned char* b_src = a_src + TcSmem<BN, STAGES>::kABytes;
+                    const unsigned char* a_src = tiles + (size_t)s * TcSmem<BN, STAGES, PAIR>::kStageBytes;
+                    const unsigned char* b_src = a_src + TcSmem<BN, STAGES, PAIR>::kABytes;
                     const uint64_t adesc = umma_desc_k_major_sw128(a_src);
                     const uint64_t bdesc = umma_desc_k_major_sw128(b_src);
 #pragma unroll
                     for (int k = 0; k < kTcBK / 16; ++k) {
                         // 16 elements of K = 32 bytes further inside the swizzle atom: +2 in 16-byte units
-                        umma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (PAIR) umma_bf16_pair(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                        else umma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
                     }
-                    umma_commit(&empty[s]);        // frees the stage when these MMAs have read it
+                    if (PAIR) umma_commit_pair(&empty[s]);
+                    else umma_commit(&empty[s]);   // frees the stage when these MMAs have read it
                 }
-                umma_commit(&acc_full[buf]);       // arrives when every MMA issued so far has finished
+                if (PAIR) umma_commit_pair(&acc_full[buf]);
+                else umma_commit(&acc_full[buf]);  // arrives when every MMA issued so far has finished
             }
         }
     } else {
@@ -225,10 +291,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;
         int local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        // the accumulator goes back to the CTA that issues the MMAs
+        auto release_accumulator = [&](int buf) {
+            if (PAIR) mbar_arrive_cluster(map_to_cta(&acc_empty[buf], 0));
+            else mbar_arrive(&acc_empty[buf]);
+        };
+        for (int tile = worker; tile < num_tiles && ok; tile += workers, ++local) {
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
-            const int m0 = (tile / n_blocks) * kTcBM, n0 = (tile % n_blocks) * kOutCols;
+            const int m0 = (tile / n_blocks) * kTileRows + (int)rank * kTcBM, n0 = (tile % n_blocks) * kOutCols;
             const int row = m0 + quarter * 32 + lane;
             ok = mbar_wait(&acc_full[buf], acc_phase);
             if (!ok && lane == 0) { atomicExch(error_flag, 3); s_abort = 1; }
@@ -249,7 +320,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld_wait();
                     if (c == 3) {
                         tcgen05_fence_before();
-                        if (lane == 0) mbar_arrive(&acc_empty[buf]);     // the accumulator has been read completely
+                        if (lane == 0) release_accumulator(buf);     // the accumulator has been read completely
                     }
                     unsigned char* panel = staging + (size_t)(c >> 1) * (kTcBM * 128) + (size_t)r_local * 128;
 #pragma unroll
@@ -295,7 +366,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         tmem_ld_wait();
                         if (half == BN / 128 - 1 && c == 3) {
                             tcgen05_fence_before();
-                            if (lane == 0) mbar_arrive(&acc_empty[buf]);     // the accumulator has been read completely
+                            if (lane == 0) release_accumulator(buf);     // the accumulator has been read completely
                         }
                         // 32 columns = 64 bytes = four 16-byte chunks of this row, in panel c / 2, chunks (c % 2) * 4 ..
                         unsigned char* panel = staging + (size_t)(c >> 1) * (kTcBM * 128) + (size_t)r_local * 128;
@@ -332,7 +403,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (c0 + 32 >= BN) {
                     // the accumulator has been read completely: hand it back before the stores
                     tcgen05_fence_before();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    if (lane == 0) release_accumulator(buf);
                 }
                 if (row < M) {
                     const int n = n0 + c0;
@@ -377,8 +448,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (TMA_STORE && threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();          // neither CTA leaves while the other may still arrive on its barriers
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
     }
 }
 
@@ -412,11 +485,12 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
     return 0;
 }
 
-template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, bool SILU = false>
+template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, bool SILU = false, bool PAIR = false>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, void* out, int ldo, int M, int N,
                      int K, int* error_flag, cudaStream_t stream, int up_offset = 0) {
-    auto kernel = gemm_tcgen05_kernel<BN, STAGES, F32OUT, TMA_STORE, SILU>;
-    constexpr int smem = TcSmem<BN, STAGES>::kTotal;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, F32OUT, TMA_STORE, SILU, PAIR>;
+    constexpr int smem = TcSmem<BN, STAGES, PAIR>::kTotal;
+    static_assert(smem <= 227 * 1024, "a CTA has 227 KB of shared memory");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -433,10 +507,33 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtenso
         if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
     }
     const int out_cols = SILU ? BN / 2 : BN, n_out = SILU ? up_offset : N;
-    const int tiles = ((n_out + out_cols - 1) / out_cols) * ((M + kTcBM - 1) / kTcBM);
-    dim3 grid(tiles < num_sms ? tiles : num_sms);
-    kernel<<<grid, 192, smem, stream>>>(ma, mw, mo, out, ldo, M, N, K, up_offset, error_flag);
-    CIB_LAUNCH_CHECK("gemm_tcgen05");
+    const int tile_rows = PAIR ? 2 * kTcBM : kTcBM;
+    const int tiles = ((n_out + out_cols - 1) / out_cols) * ((M + tile_rows - 1) / tile_rows);
+    if (!PAIR) {
+        dim3 grid(tiles < num_sms ? tiles : num_sms);
+        kernel<<<grid, 192, smem, stream>>>(ma, mw, mo, out, ldo, M, N, K, up_offset, error_flag);
+        CIB_LAUNCH_CHECK("gemm_tcgen05");
+        return 0;
+    }
+    // clusters of two CTAs, one pair per tile at a time
+    const int pairs = tiles < num_sms / 2 ? tiles : num_sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mw, mo, out, ldo, M, N, K, up_offset, error_flag);
+    if (e != cudaSuccess) {
+        set_error("gemm_tcgen05: launch of CTA pairs failed: %s", cudaGetErrorString(e));
+        return -2;
+    }
     return 0;
 }
 
@@ -458,6 +555,11 @@ extern "C" int cib_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, 
     CIB_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
     CIB_REQUIRE(ldo >= (silu_pair ? N / 2 : N) && error_flag != nullptr, "gemm_tcgen05: bad output arguments");
     CUtensorMap ma, mw;
+    // From 256 rows on, pairs of CTAs share 256-row tiles (CUINFER_B200_GEMM_PAIR=0 keeps one CTA per tile, for comparisons).
+    static const bool pair_allowed = [] { const char* e = getenv("CUINFER_B200_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    // (only when there are enough 256-row tiles for every pair of SMs: with fewer, one CTA per 128-row tile measured faster)
+    const int pair_tiles = ((M + 255) / 256) * (((silu_pair ? N / 2 : N) + 127) / 128);
+    const bool pair = pair_allowed && M >= 256 && pair_tiles >= 74;
     if (silu_pair) {
         const int half = N / 2;
         CIB_REQUIRE(N % 2 == 0 && !out_f32 && ldo % 8 == 0 && ((uintptr_t)out % 16) == 0,
@@ -466,7 +568,26 @@ extern "C" int cib_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, 
         if (make_map(&ma, a, M, K, lda, kTcBM) != 0 || make_map(&mw, w, N, K, ldw, 128) != 0 ||
             make_map(&mo, out, M, half, ldo, kTcBM) != 0)
             return -1;
+        if (pair) return launch_tc<256, 6, false, true, true, true>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream, half);
         return launch_tc<256, 4, false, true, true>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream, half);
+    }
+    if (pair) {
+        // 256 x 256 tiles when those still give most pairs a tile, else 256 x 128; a CTA loads half of a tile's weight rows
+        const int m_pairs = (M + 255) / 256;
+        const int bn2 = (N % 256 == 0 && (N / 256) * m_pairs >= 60) ? 256 : 128;
+        const bool tma_out2 = !out_f32 && ldo % 8 == 0 && ((uintptr_t)out % 16) == 0;
+        CUtensorMap mo2;
+        if (make_map(&ma, a, M, K, lda, kTcBM) != 0 || make_map(&mw, w, N, K, ldw, bn2 / 2) != 0) return -1;
+        mo2 = ma;
+        if (tma_out2 && make_map(&mo2, out, M, N, ldo, kTcBM) != 0) return -1;
+        if (bn2 == 256) {
+            if (out_f32) return launch_tc<256, 6, true, false, false, true>(ma, mw, mo2, out, ldo, M, N, K, error_flag, stream);
+            if (tma_out2) return launch_tc<256, 6, false, true, false, true>(ma, mw, mo2, out, ldo, M, N, K, error_flag, stream);
+            return launch_tc<256, 6, false, false, false, true>(ma, mw, mo2, out, ldo, M, N, K, error_flag, stream);
+        }
+        if (out_f32) return launch_tc<128, 8, true, false, false, true>(ma, mw, mo2, out, ldo, M, N, K, error_flag, stream);
+        if (tma_out2) return launch_tc<128, 8, false, true, false, true>(ma, mw, mo2, out, ldo, M, N, K, error_flag, stream);
+        return launch_tc<128, 8, false, false, false, true>(ma, mw, mo2, out, ldo, M, N, K, error_flag, stream);
     }
     // Tile width: 256 when that still gives most SMs a tile, else 128.
     const int m_blocks = (M + 127) / 128;
