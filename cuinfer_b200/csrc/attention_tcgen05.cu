@@ -6,17 +6,19 @@
 //
 //   * a CTA owns a 128-row query tile (128 / g tokens x g heads of one kv head) and walks over 128-key tiles;
 //   * keys and values come page by page through TMA (`cp.async.bulk.tensor.2d`, one box of 64 columns x one page per
-//     copy, 128-byte swizzle: the layout the tensor cores read), issued by the lanes of one producer warp in parallel,
+//     copy, 128-byte swizzle: the layout the tensor cores read), issued by the lanes of the producer warps,
 //     double-buffered, completion counted in bytes on mbarriers.  (Copies issued by ordinary loads or `cp.async` kept
 //     too few bytes in flight per SM: a tile took longer to arrive than its softmax takes.)  The page size must be a
 //     power of two of at least 8 slots, so that a box starts on a 1024-byte swizzle atom;
-//   * S = Q K^T and O += P V are `tcgen05.mma.cta_group::1.kind::f16` with accumulators in tensor memory: two S
-//     buffers (128 columns each) and O (128 columns); K is a K-major operand, V an MN-major one, straight from the
-//     page layout;
-//   * four warps do the softmax, one thread per row (TMEM lane = row): they read S with `tcgen05.ld`, keep a running
-//     maximum in base 2 that is only raised when it grows by more than 8 (so O in tensor memory is rescaled rarely,
-//     with `tcgen05.ld`/`tcgen05.st`), write P in bfloat16 to a swizzled shared-memory tile (the A operand of P V);
-//   * a fifth warp's first lane issues the MMAs; S of tile j+1 is computed while the softmax of tile j runs.
+//   * S = Q K^T and O += P V are `tcgen05.mma.cta_group::1.kind::f16` with accumulators in tensor memory; K is a
+//     K-major operand, V an MN-major one, straight from the page layout; P is the A operand of P V straight from tensor
+//     memory (bfloat16, written with `tcgen05.st` over the scores it was made from), so it never touches shared memory;
+//   * key tiles alternate between two softmax groups of eight warps, each with its own S, running maximum, running sum
+//     and O in tensor memory (4 x 128 columns), merged at the end like the splits of a split-key kernel: while one group
+//     waits for its scores or its P V, the other computes exponentials.  Inside a group two threads share a row (TMEM
+//     lane = row, 64 columns each): they read S with one `tcgen05.ld` pass, keep the running maximum in base 2 and raise
+//     it only when it grows by more than 8 (so O is rescaled rarely, with `tcgen05.ld`/`tcgen05.st`);
+//   * a seventeenth warp's first lane issues the MMAs; S of tile j+1 is computed while the softmax of tile j runs.
 //
 // Every mbarrier wait is bounded; on a time-out the kernel raises the error flag, stops, frees its tensor memory
 // and returns.
@@ -100,11 +102,20 @@ __device__ __forceinline__ void tst32(uint32_t taddr, const uint32_t (&r)[32]) {
 __device__ __forceinline__ void tld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tst_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// shared memory: Q | K0 | K1 | V0 | V1 | P, each 128 rows x 128 columns bf16 = 32 KB as two 64-column panels
+// shared memory: Q | K0 | K1 | V0 | V1, each 128 rows x 128 columns bf16 = 32 KB as two 64-column panels.  (A third key
+// buffer changed nothing: what a tile waits for is the 64 KB of its keys and values crossing from the L2.)
 constexpr int kTileBytes = 2 * kPanel;
-constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;
+constexpr int kKBufs = 2, kVBufs = 2;
+constexpr int kSmemBytes = (1 + kKBufs + kVBufs) * kTileBytes + 1024 + 256;
 
-constexpr int kThreads = 352;     // 8 softmax warps, 1 MMA warp, a producer warp for keys and one for values
+constexpr int kMmaWarp = 16;                       // warps 0-15: two softmax groups of eight
+constexpr int kThreads = (kMmaWarp + 3) * 32;      // + the MMA warp, a producer warp for keys and one for values
+
+// A operand from tensor memory (P, bfloat16, two keys to a column), B from shared memory
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a_tmem), "l"(b), "r"(id), "r"(acc) : "memory");
+}
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
     asm volatile(
@@ -121,21 +132,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sQ = base;
-    unsigned char* sK = base + kTileBytes;          // two buffers
-    unsigned char* sV = base + 3 * kTileBytes;      // two buffers
-    unsigned char* sP = base + 5 * kTileBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * kTileBytes);
-    uint64_t* k_full = bars;           // [2]  a key tile has landed (bytes counted)
-    uint64_t* v_full = bars + 2;       // [2]  a value tile has landed
-    uint64_t* s_full = bars + 4;       // [2]  S of a tile is in tensor memory
-    uint64_t* p_ready = bars + 6;      //      P of a tile is in shared memory
-    uint64_t* pv_done = bars + 7;      //      O includes a tile
-    uint64_t* k_free = bars + 8;       // [2]  S has read a key buffer (early: keys two tiles ahead can be fetched)
-    uint64_t* v_free = bars + 10;      // [2]  P V has read a value buffer
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    unsigned char* sK = base + kTileBytes;                      // kKBufs buffers: tile j in buffer j % kKBufs
+    unsigned char* sV = base + (1 + kKBufs) * kTileBytes;       // kVBufs buffers
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + (1 + kKBufs + kVBufs) * kTileBytes);
+    // one barrier per buffer; key tile j uses value buffer, tensor-memory half and softmax group j % 2
+    uint64_t* k_full = bars;           // [kKBufs <= 3] a key tile has landed (bytes counted)
+    uint64_t* v_full = bars + 3;       // [2] a value tile has landed
+    uint64_t* s_full = bars + 5;       // [2] S of a tile is in tensor memory
+    uint64_t* p_ready = bars + 7;      // [2] P of a tile is in tensor memory (8 warps arrive)
+    uint64_t* pv_done = bars + 9;      // [2] the group's O includes a tile
+    uint64_t* k_free = bars + 11;      // [kKBufs <= 3] S has read a key buffer (early: its next keys can be fetched)
+    uint64_t* v_free = bars + 14;      // [2] P V has read a value buffer
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     __shared__ int s_req, s_tile, s_abort;
-    __shared__ float s_mx[2][2][128];      // [tile parity][column half][row]: the halves' maxima of a row
-    __shared__ float s_l[2][128];          // [column half][row]: the halves' sums at the end
+    __shared__ float s_mx[2][2][2][128];   // [group][tile parity within the group][column half][row]: the halves' maxima
+    __shared__ float s_l[2][2][128];       // [group][column half][row]: the halves' sums at the end
+    __shared__ float s_m[2][128];          // [group][row]: the group's reference maximum at the end
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.y;
@@ -149,21 +161,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             t -= tiles;
         }
         s_req = r; s_tile = t; s_abort = 0;
+        for (int i = 0; i < kKBufs; ++i) { bar_init(&k_full[i], 1); bar_init(&k_free[i], 1); }
         for (int i = 0; i < 2; ++i) {
-            bar_init(&k_full[i], 1); bar_init(&v_full[i], 1); bar_init(&s_full[i], 1);
-            bar_init(&k_free[i], 1); bar_init(&v_free[i], 1);
+            bar_init(&v_full[i], 1); bar_init(&v_free[i], 1); bar_init(&s_full[i], 1);
+            bar_init(&p_ready[i], 8); bar_init(&pv_done[i], 1);
         }
-        bar_init(p_ready, 8);
-        bar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 8) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // stale shared memory must at least be finite: rows of a tile that no page covers are multiplied by P = 0
-    for (int i = tid; i < 4 * kTileBytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(sK)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < (kKBufs + kVBufs) * kTileBytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(sK)[i] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // before the bulk copies write the same bytes
     fence_before();
     __syncthreads();
@@ -185,9 +196,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
         num_tiles = (pos_last + 1 - k_lo + kN - 1) / kN;
     }
 
-    if (active && warp < 8) {
+    if (active && warp < kMmaWarp) {
         // ---- the query tile: row = token_local * g + head_in_group, two swizzled 64-column panels ----
-        for (int idx = tid; idx < kM * 16; idx += 256) {
+        for (int idx = tid; idx < kM * 16; idx += kMmaWarp * 32) {
             const int row = idx >> 4, c = idx & 15;
             const int grow = row0 + row;
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -201,19 +212,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
     }
     __syncthreads();
 
-    if (active && warp == 8) {
+    // tensor memory: S of group 0 | S of group 1 | O of group 0 | O of group 1, 128 columns each; P of a group (bfloat16,
+    // two keys to a column) takes the first 64 columns of the group's S once the softmax holds S in registers
+    if (active && warp == kMmaWarp) {
         // ---- the MMAs: the whole warp walks the loop, lane 0 issues ----
         auto issue_s = [&](int j) {
             if (lane != 0) return;
             const int b = j & 1;
-            const uint64_t qd = desc_kmajor(sQ), kd = desc_kmajor(sK + b * kTileBytes);
+            const uint64_t qd = desc_kmajor(sQ), kd = desc_kmajor(sK + (j % kKBufs) * kTileBytes);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const uint64_t off = (uint64_t)(((k >> 2) * kPanel + (k & 3) * 32) >> 4);
                 mma(tmem + (uint32_t)(b * kN), qd + off, kd + off, idesc(false), k != 0);
             }
             commit(&s_full[b]);
-            commit(&k_free[b]);             // the key buffer can be refilled as soon as S has been computed
+            commit(&k_free[j % kKBufs]);    // the key buffer can be refilled as soon as S has been computed
         };
         auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
             bool ok = bar_wait(bar, parity);
@@ -224,13 +237,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
         ok = wait_all(&k_full[0], 0, 11);
         if (ok) { fence_after(); issue_s(0); }
         for (int j = 0; j < num_tiles && ok; ++j) {
+            const int b = j & 1;
+            const uint32_t parity = (j >> 1) & 1;
             if (j + 1 < num_tiles) {
-                ok = wait_all(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 12);
+                // S(j+1) overwrites S and P of tile j-1 (same group): P V(j-1) was issued before, and the tensor pipe
+                // runs what one thread issues in order
+                ok = wait_all(&k_full[(j + 1) % kKBufs], ((j + 1) / kKBufs) & 1, 12);
                 if (!ok) break;
                 fence_after();
                 issue_s(j + 1);
             }
-            ok = wait_all(p_ready, j & 1, 13) && wait_all(&v_full[j & 1], (j >> 1) & 1, 14);
+            ok = wait_all(&p_ready[b], parity, 13) && wait_all(&v_full[b], parity, 14);
             if (!ok) break;
             {
                 // the last page of the request came whole: value rows past its last token may hold anything, and
@@ -239,7 +256,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                 if (valid_rows < kN) {
                     const int box_rows = min(page_size, kN);
                     const int end = min(kN, (valid_rows + box_rows - 1) / box_rows * box_rows);
-                    unsigned char* vb = sV + (j & 1) * kTileBytes;
+                    unsigned char* vb = sV + b * kTileBytes;
                     for (int idx = valid_rows * 16 + lane; idx < end * 16; idx += 32) {
                         const int row = idx >> 4, c = idx & 15;
                         *reinterpret_cast<uint4*>(vb + (c >> 3) * kPanel + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
@@ -250,38 +267,39 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             }
             fence_after();
             if (lane == 0) {
-                const int b = j & 1;
-                const uint64_t pd = desc_kmajor(sP);
+                // O_b += P V: P is the A operand straight from tensor memory (16 keys = 8 columns per step)
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    const uint64_t aoff = (uint64_t)(((k >> 2) * kPanel + (k & 3) * 32) >> 4);
                     const uint64_t vd = desc_mnmajor(sV + b * kTileBytes + k * 16 * 128, kPanel);
-                    mma(tmem + 2u * kN, pd + aoff, vd, idesc(true), (j | k) != 0);
+                    mma_ts(tmem + (uint32_t)(2 * kN + b * kN), tmem + (uint32_t)(b * kN + k * 8), vd, idesc(true), (j >= 2) || k != 0);
                 }
-                commit(pv_done);
+                commit(&pv_done[b]);
                 commit(&v_free[b]);         // the value buffer can be refilled
             }
             __syncwarp();
         }
-    } else if (active && warp >= 9) {
-        // ---- producer warps (9: keys, 10: values): a lane issues one TMA copy per (page of the tile, 64-column panel); keys of tile j+2 as
-        // soon as S(j) has read the buffer, values after P V(j).  Rows of a tile past the request's last page are not
-        // copied: their columns of S are masked and P is 0 there.  A page number outside the pool turns into a row
-        // outside the tensor map, which reads as zeros and still counts its bytes. ----
+    } else if (active && warp > kMmaWarp) {
+        // ---- producer warps (first: keys, second: values; two more warps did not make the copies of a tile land sooner:
+        // 64 KB per tile is what an SM fetches from the L2 in about 1.6 k cycles): a lane issues one TMA copy per (page
+        // of the tile, 64-column panel); keys of tile j+2 as soon as S(j) has read its buffer, values of tile j+2 after P V(j).  Rows of a tile past the
+        // request's last page are not copied: their columns of S are masked and P is 0 there.  A page number outside the
+        // pool turns into a row outside the tensor map, which reads as zeros and still counts its bytes. ----
         const int* table = block_table + (size_t)r * table_stride;
         const int box_rows = min(page_size, kN);
         const int boxes = kN / box_rows;
         const long long total_rows = (long long)num_pages * 2 * nkv * page_size;
         // a tile has at most 32 boxes (16 pages of 8 slots x 2 panels): lane = box * 2 + panel.  The page number of
         // a lane's box is fetched a tile ahead, so that no copy waits for a round trip to the table.
+        const int kv = warp - kMmaWarp - 1;
         const int box = lane >> 1, panel = lane & 1;
         int page = -1;
         auto lookup = [&](int t) {
             const int key = k_lo + t * kN + box * box_rows;
             page = t < num_tiles && box < boxes && key < seq_len ? __ldg(table + key / page_size) : -1;
         };
-        auto fill = [&](int t, int kv) {
-            const int b = t & 1;
+        const int depth = kv ? kVBufs : kKBufs;
+        auto fill = [&](int t) {
+            const int b = t % depth;
             const int key0 = k_lo + t * kN;
             uint64_t* bar = kv ? &v_full[b] : &k_full[b];
             const int nvalid = min(boxes, max(0, (seq_len - key0 + box_rows - 1) / box_rows));
@@ -299,35 +317,40 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             if (!ok && lane == 0) { atomicExch(error_flag, code); s_abort = 1; }
             return __all_sync(0xffffffffu, ok);
         };
-        const int kv = warp - 9;
         uint64_t* free_bar = kv ? v_free : k_free;
-        lookup(0);
-        fill(0, kv);
-        lookup(1);
-        if (num_tiles > 1) fill(1, kv);
-        lookup(2);
-        for (int j = 0; j + 2 < num_tiles; ++j) {
-            if (!wait_all(&free_bar[j & 1], (j >> 1) & 1, 18 + kv)) break;      // S(j) / P V(j) has read the buffer
-            fill(j + 2, kv);
-            lookup(j + 3);
+        for (int t = 0; t < depth && t < num_tiles; ++t) {
+            lookup(t);
+            fill(t);
         }
-    } else if (active && warp < 8) {
-        // ---- softmax: two threads per row (TMEM lane), each takes 64 of the 128 columns; warps w and w + 4 share
-        // the lanes 32 * (w % 4) .. + 31 and meet at a named barrier to combine a row's maxima ----
-        const int quarter = warp & 3, half = warp >> 2;
+        lookup(depth);
+        for (int j = 0; j + depth < num_tiles; ++j) {
+            if (!wait_all(&free_bar[j % depth], (j / depth) & 1, 18 + kv)) break;      // S(j) / P V(j) has read the buffer
+            fill(j + depth);
+            lookup(j + depth + 1);
+        }
+    } else if (active && warp < kMmaWarp) {
+        // ---- softmax: group grp (warps 8 grp .. 8 grp + 7) takes the key tiles j = grp, grp + 2, ... with a running
+        // maximum, a running sum and an output accumulator of its own, so that one group's exponentials run while the
+        // other waits for its scores or its P V; the two are merged at the end.  Two threads per row (TMEM lane), each
+        // takes 64 of the 128 columns; warps w and w + 4 of a group share the lanes 32 * (w % 4) .. + 31 and meet at a
+        // named barrier to combine a row's maxima. ----
+        const int grp = warp >> 3;
+        const int quarter = warp & 3, half = (warp >> 2) & 1;
         const int cb = half * 64;
         const int row_local = quarter * 32 + lane;
         const int grow = row0 + row_local;
         const bool row_ok = grow < rows_total;
         const int pos = row_ok ? seq_len - n + grow / g : -1;
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-        auto pair_barrier = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
+        const uint32_t s_col = (uint32_t)(grp * kN), o_col = (uint32_t)(2 * kN + grp * kN);
+        auto pair_barrier = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + grp * 4 + quarter) : "memory"); };
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < num_tiles; ++j) {
-            const int b = j & 1;
+        int done = 0;                               // tiles this group has finished
+        for (int j = grp; j < num_tiles; j += 2, ++done) {
+            const uint32_t parity = (uint32_t)(done & 1);
             const int key0 = k_lo + j * kN;
-            ok = bar_wait(&s_full[b], (j >> 1) & 1);
+            ok = bar_wait(&s_full[grp], parity);
             if (!ok && lane == 0) { atomicExch(error_flag, 15); s_abort = 1; }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
             if (!ok) break;
@@ -338,8 +361,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             // this thread's 64 scores, read from tensor memory once; masked ones become -inf here, so that the
             // maximum (the scale is positive: applied afterwards) and the exponentials need no second look at the mask
             uint32_t v[64];
-            tld32(lane_addr + (uint32_t)(b * kN + cb), *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-            tld32(lane_addr + (uint32_t)(b * kN + cb + 32), *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            tld32(lane_addr + s_col + (uint32_t)cb, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            tld32(lane_addr + s_col + (uint32_t)(cb + 32), *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
             tld_wait();
             float mx = -INFINITY;
             if (need_mask) {
@@ -351,9 +374,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             }
 #pragma unroll
             for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-            s_mx[j & 1][half][row_local] = mx;
-            pair_barrier();
-            mx = fmaxf(s_mx[j & 1][0][row_local], s_mx[j & 1][1][row_local]) * scale_log2;
+            s_mx[grp][done & 1][half][row_local] = mx;
+            pair_barrier();                         // both threads of the row hold their scores in registers from here on
+            mx = fmaxf(s_mx[grp][done & 1][0][row_local], s_mx[grp][done & 1][1][row_local]) * scale_log2;
             // raise the reference maximum only when it would grow by more than 8 (values stay below 2^8); both
             // threads of a row see the same numbers and decide alike
             float corr = 1.f;
@@ -362,9 +385,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                 corr = m_used == -INFINITY ? 0.f : exp2f(m_used - mx);
                 m_used = mx;
                 l *= corr;
-                rescale = j > 0;
+                rescale = done > 0;
             }
-            // pass 2: P = 2^(s * scale - m): one fused multiply-add and one ex2 per score, packed two to a register
+            // P = 2^(s * scale - m): one fused multiply-add and one ex2 per score, packed two to a register
             const float m_eff = m_used == -INFINITY ? 0.f : m_used;
             uint32_t p[32];
 #pragma unroll
@@ -379,84 +402,87 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                 __nv_bfloat162 pk = __floats2bfloat162_rn(pe[0], pe[1]);
                 p[e / 2] = *reinterpret_cast<uint32_t*>(&pk);
             }
-            // O and the P tile are free once P V of the tile before has finished
-            if (j > 0) {
-                ok = bar_wait(pv_done, (j - 1) & 1);
+            // the group's O is only touched once P V of its tile before has finished
+            if (done > 0 && __any_sync(0xffffffffu, rescale)) {
+                ok = bar_wait(&pv_done[grp], (uint32_t)((done - 1) & 1));
                 if (!ok && lane == 0) { atomicExch(error_flag, 16); s_abort = 1; }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
                 fence_after();
-            }
-            if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
                 for (int c = 0; c < 2; ++c) {
-                    uint32_t v[32];
-                    tld32(lane_addr + (uint32_t)(2 * kN + cb + c * 32), v);
+                    uint32_t o[32];
+                    tld32(lane_addr + o_col + (uint32_t)(cb + c * 32), o);
                     tld_wait();
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * (rescale ? corr : 1.f));
-                    tst32(lane_addr + (uint32_t)(2 * kN + cb + c * 32), v);
+                    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * (rescale ? corr : 1.f));
+                    tst32(lane_addr + o_col + (uint32_t)(cb + c * 32), o);
                 }
-                tst_wait();
             }
-            // this thread's 64 keys are panel `half` of the P tile
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint4 v = make_uint4(p[4 * c], p[4 * c + 1], p[4 * c + 2], p[4 * c + 3]);
-                *reinterpret_cast<uint4*>(sP + half * kPanel + row_local * 128 + ((c ^ (row_local & 7)) << 4)) = v;
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // P: this thread's 64 keys are 32 columns behind the 32 of the row's other thread, over the scores that
+            // both threads hold in registers since the barrier above
+            tst32(lane_addr + s_col + (uint32_t)(half * 32), p);
+            tst_wait();
             fence_before();
             __syncwarp();
-            if (lane == 0) bar_arrive(p_ready);
+            if (lane == 0) bar_arrive(&p_ready[grp]);
         }
-        // ---- O / l -> global ----
-        if (ok && num_tiles > 0) {
-            ok = bar_wait(pv_done, (num_tiles - 1) & 1);
+        // ---- merge the two groups: O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)) ----
+        if (ok && done > 0) {
+            ok = bar_wait(&pv_done[grp], (uint32_t)((done - 1) & 1));
             if (!ok && lane == 0) { atomicExch(error_flag, 17); s_abort = 1; }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
-        s_l[half][row_local] = l;
-        pair_barrier();
-        if (ok && num_tiles > 0) {
-            fence_after();
-            l = s_l[0][row_local] + s_l[1][row_local];
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = nullptr;
+        s_l[grp][half][row_local] = l;
+        if (half == 0) s_m[grp][row_local] = m_used;
+        fence_before();
+        asm volatile("bar.sync 9, %0;" ::"r"(kMmaWarp * 32) : "memory");      // the sixteen softmax warps
+        fence_after();
+        if (!(*(volatile int*)&s_abort) && num_tiles > 0) {
+            // group grp stores the output columns 32 grp .. + 31 of this thread's half of the head
+            const float m0 = s_m[0][row_local], m1 = s_m[1][row_local];
+            const float l0 = s_l[0][0][row_local] + s_l[0][1][row_local], l1 = s_l[1][0][row_local] + s_l[1][1][row_local];
+            const float m = fmaxf(m0, m1);
+            const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - m);
+            const float total = l0 * w0 + l1 * w1;
+            const float inv = total > 0.f ? 1.f / total : 0.f;
+            const float f0 = w0 * inv, f1 = w1 * inv;
+            const bool has1 = num_tiles > 1;        // group 1 has an accumulator only if there was a second tile
+            uint32_t a[32], b[32];
+            tld32(lane_addr + (uint32_t)(2 * kN + cb + grp * 32), a);
+            if (has1) tld32(lane_addr + (uint32_t)(3 * kN + cb + grp * 32), b);
+            tld_wait();
             if (row_ok) {
-                const int tl = grow / g, hi = grow % g;
-                dst = out + (size_t)(q0 + tl) * out_stride + (size_t)(kvh * g + hi) * kD + cb;
-            }
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tld32(lane_addr + (uint32_t)(2 * kN + cb + c * 32), v);
-                tld_wait();
-                if (row_ok) {
+                const int tl = grow / g, hh = grow % g;
+                __nv_bfloat16* dst = out + (size_t)(q0 + tl) * out_stride + (size_t)(kvh * g + hh) * kD + cb + grp * 32;
 #pragma unroll
-                    for (int e = 0; e < 32; e += 8) {
-                        uint4 pk;
-                        __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
-                        __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
-                        __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
-                        __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
-                        pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
-                        pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
-                        *reinterpret_cast<uint4*>(dst + c * 32 + e) = pk;
+                for (int e = 0; e < 32; e += 8) {
+                    float y[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        y[u] = __uint_as_float(a[e + u]) * f0;
+                        if (has1) y[u] = fmaf(__uint_as_float(b[e + u]), f1, y[u]);
                     }
+                    uint4 pk;
+                    __nv_bfloat162 t0 = __floats2bfloat162_rn(y[0], y[1]), t1 = __floats2bfloat162_rn(y[2], y[3]);
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(y[4], y[5]), t3 = __floats2bfloat162_rn(y[6], y[7]);
+                    pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
+                    pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
+                    *reinterpret_cast<uint4*>(dst + e) = pk;
                 }
             }
         }
     }
     fence_before();
     __syncthreads();
-    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    if (warp == kMmaWarp) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
 }
 
 }  // namespace fa
 }  // namespace cib
 
 using namespace cib;
+
 
 extern "C" int cib_attention_tcgen05_supports(int head_dim, int nq, int nkv, int page_size) {
     if (head_dim != 128 || nkv <= 0 || nq % nkv != 0) return 0;
