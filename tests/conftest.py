@@ -43,10 +43,16 @@ TINY_B = _cfg(num_hidden_layers=3, hidden_size=96, num_attention_heads=8, num_ke
 TINY_C = _cfg(num_hidden_layers=1, hidden_size=80, num_attention_heads=6, num_key_value_heads=3, head_dim=48,
               intermediate_size=176, vocab_size=517, rope_theta=500000.0, rms_norm_eps=3e-6,
               tie_word_embeddings=False, max_position_embeddings=1536)
+# head size 128 with two query heads per kv head: the shape that the tensor-core attention kernels and, from 128 rows
+# on, the tcgen05 projections take in bfloat16 (A, B and C run on the all-sizes kernels)
+TINY_D = _cfg(num_hidden_layers=2, hidden_size=192, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+              intermediate_size=448, vocab_size=777, rope_theta=1000000.0, rms_norm_eps=1e-6,
+              tie_word_embeddings=True, max_position_embeddings=1024, eos_token_id=5)
 
 TINY = {"A": (TINY_A, dict(seed=0, std=0.05, gain_std=0.0, block_size=16)),
         "B": (TINY_B, dict(seed=1, std=0.04, gain_std=0.1, block_size=32)),
-        "C": (TINY_C, dict(seed=2, std=0.06, gain_std=0.2, block_size=16))}
+        "C": (TINY_C, dict(seed=2, std=0.06, gain_std=0.2, block_size=16)),
+        "D": (TINY_D, dict(seed=3, std=0.05, gain_std=0.1, block_size=16))}
 
 # Largest |engine - plain| allowed, as a fraction of the largest |plain logit| of the sequence.
 # float32: both sides compute in 32 bits; only the order of sums differs.

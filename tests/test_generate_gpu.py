@@ -42,7 +42,7 @@ def test_greedy_generation_float32_equals_plain(model_folders, name):
     assert not llm.engine.runner.manager.live_requests()
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_greedy_generation_bfloat16_is_near_best(model_folders, name):
     from cuinfer_b200 import LLM, SamplingParams
 

@@ -18,7 +18,7 @@ from conftest import ROOT, TOLERANCE, random_tokens
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["A", "B", "C"]
+NAMES = ["A", "B", "C", "D"]
 
 
 def _requests(cfg, lengths, seed):
@@ -89,6 +89,18 @@ def test_first_tokens_of_a_sequence(model_folders, dtype, tmp_path):
     cfg = model_folders["B"][1]
     requests = _requests(cfg, [1, 2, 3], seed=6)
     _run(model_folders, "B", dtype, traces.tail_decode(requests, 3), requests, tmp_path)
+
+
+def test_decode_through_tma_and_long_prompts(model_folders, tmp_path, monkeypatch):
+    """The head-128 model in bfloat16 with the decode kernel forced onto its TMA path (the engine keeps short key
+    streams on cp.async) and prompts of several row tiles: whole, then cut into portions beside decoded tokens."""
+    from cuinfer_b200 import kernels
+    monkeypatch.setattr(kernels, "DECODE_TMA_MIN_KEYS", 0)
+    cfg = model_folders["D"][1]
+    requests = _requests(cfg, [300, 170, 45, 260], seed=8)
+    _run(model_folders, "D", "bfloat16", traces.tail_decode(requests, 40), requests, tmp_path)
+    steps = traces.mixed(requests, max_live=3, sizes=(130, 2, 40, 3, 150, 7))
+    _run(model_folders, "D", "bfloat16", steps, requests, tmp_path, max_tokens=traces.live_token_peak(steps))
 
 
 def test_trace_run_program(model_folders, tmp_path):
