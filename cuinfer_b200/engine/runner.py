@@ -106,7 +106,7 @@ class ModelRunner:
                 self._run_cache[run] = (src, src == run)
         self._ring = _PinnedRing()
         self._arena: Optional[torch.Tensor] = None
-        self._graphs: Dict[int, "DecodeGraph"] = {}
+        self._graphs: Dict[tuple, "DecodeGraph"] = {}        # (rows bucket, context class) -> graph
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -328,19 +328,25 @@ class ModelRunner:
 
     # ---- decode steps as CUDA graphs ---------------------------------------------------------------------
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+    # A graph is also captured per class of context length: how the decode attention kernel splits the keys over
+    # CTAs is fixed at capture, and a split chosen for the model's longest context is a poor one for short ones.
+    GRAPH_CONTEXTS = (512, 2048, 8192, 32768, 131072)
 
     def can_use_graph(self, entries: Sequence[StepEntry]) -> bool:
         return (self.config.enable_cuda_graph and len(entries) <= self.GRAPH_BUCKETS[-1]
                 and all(len(e.tokens) == 1 for e in entries))
 
-    def decode_graph(self, rows: int) -> "DecodeGraph":
+    def decode_graph(self, rows: int, longest: Optional[int] = None) -> "DecodeGraph":
+        """The graph for ``rows`` requests whose longest context (this step's token included) is ``longest``."""
         bucket = next(b for b in self.GRAPH_BUCKETS if b >= rows)
-        graph = self._graphs.get(bucket)
+        longest = self.max_model_len if longest is None else longest
+        context = min(self.max_model_len, next((c for c in self.GRAPH_CONTEXTS if c >= longest), self.max_model_len))
+        graph = self._graphs.get((bucket, context))
         if graph is None:
             stride = (self.max_model_len + self.page_size - 1) // self.page_size
-            graph = DecodeGraph(self, bucket, stride)
+            graph = DecodeGraph(self, bucket, stride, context)
             graph.capture()
-            self._graphs[bucket] = graph
+            self._graphs[(bucket, context)] = graph
         return graph
 
     def decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -348,8 +354,10 @@ class ModelRunner:
         Returns float32 logits ``[len(entries), vocab]``; the tensor is overwritten by the next decode step."""
         self._validate_decode(entries)
         self.storage.zero_slots(self.manager.take_newly_admitted())
-        graph = self.decode_graph(len(entries))
-        graph.upload(entries)
+        mgr = self.manager
+        starts = [mgr.num_tokens(e.request_id) for e in entries]
+        graph = self.decode_graph(len(entries), max(starts) + 1)
+        graph.upload(entries, starts)
         logits = graph.replay()
         for e in entries:
             self.manager.commit(e.request_id, 1)
@@ -372,10 +380,11 @@ class DecodeGraph:
     All per-step inputs live in one device arena that is refreshed by a single copy from pinned memory.
     """
 
-    def __init__(self, runner: "ModelRunner", rows: int, table_stride: int) -> None:
+    def __init__(self, runner: "ModelRunner", rows: int, table_stride: int, context: Optional[int] = None) -> None:
         self._runner = weakref.ref(runner)       # no cycle: a dropped engine frees its graphs at once
         self.rows = rows
         self.stride = table_stride
+        self.context = context or runner.max_model_len      # the context length the kernels' launch shapes are chosen for
         G = len(runner.groups)
         B, P = rows, table_stride
         self.layout = {}
@@ -437,7 +446,7 @@ class DecodeGraph:
             num_tokens=B, num_requests=B, token_ids=self._dev("tok"), positions=self._dev("pos"),
             token_request=self._dev("treq"), query_start_loc=self._dev("qsl"), seq_lens=self._dev("sl"),
             state_slots=self._dev("slots"), query_start_loc_host=list(range(B + 1)), seq_lens_host=[],
-            state_slots_host=[], max_query_len=1, max_seq_len=r.max_model_len, groups=groups, decode_only=True)
+            state_slots_host=[], max_query_len=1, max_seq_len=self.context, groups=groups, decode_only=True)
         for run, (src, writes) in r._run_cache.items():
             ctx.kv[run] = PagedKV(r.storage.run_cache[src], groups[r.storage.run_group[src]], writes)
         ctx.state = r.storage.state
@@ -447,7 +456,7 @@ class DecodeGraph:
         stream = self.runner.model.forward(self.ctx)
         return self.runner.model.logits(stream, self._dev("want"))
 
-    def upload(self, entries: Sequence[StepEntry]) -> None:
+    def upload(self, entries: Sequence[StepEntry], starts: Optional[List[int]] = None) -> None:
         r = self.runner
         mgr = r.manager
         i = self.turn
@@ -458,7 +467,8 @@ class DecodeGraph:
         B, P, ps = self.rows, self.stride, r.page_size
         n = len(entries)
         tok, pos, sl, slots = (self._view(host, k) for k in ("tok", "pos", "sl", "slots"))
-        starts = [mgr.num_tokens(e.request_id) for e in entries]
+        if starts is None:
+            starts = [mgr.num_tokens(e.request_id) for e in entries]
         tok[:n] = [e.tokens[0] for e in entries]
         tok[n:] = 0
         pos[:n] = starts

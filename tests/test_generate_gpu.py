@@ -97,6 +97,29 @@ def test_eos_stops_and_is_returned(model_folders):
         assert go_on.finish_reason == "length" and go_on.token_ids == free_run
 
 
+def test_decode_graphs_per_context_class(model_folders):
+    """Decoding across a context-class boundary (512) switches to another captured graph; the tokens are those of
+    the plain implementation, in 32-bit and (near-best) on the head-128 model in bfloat16."""
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders["B"]
+    pcfg, weights = plain_qwen3.load_folder(folders["float32"])
+    prompts = [random_tokens(cfg["vocab_size"], n, 70 + i) for i, n in enumerate([505, 40])]
+    llm = LLM(folders["float32"], dtype="float32", block_size=block, num_blocks=40, max_num_seqs=4)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    for prompt, res in zip(prompts, out):
+        assert res.token_ids == plain_qwen3.greedy_generate(pcfg, weights, prompt, 12)
+    keys = sorted(llm.engine.runner._graphs)
+    assert {k[1] for k in keys} == {512, cfg["max_position_embeddings"]}, keys       # 512, then 2048 capped by the model
+    folders, cfg, block = model_folders["D"]
+    pcfg, weights = plain_qwen3.load_folder(folders["bfloat16"])
+    prompt = random_tokens(cfg["vocab_size"], 508, 77)
+    llm = LLM(folders["bfloat16"], dtype="bfloat16", block_size=block, num_blocks=40, max_num_seqs=2)
+    res = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))[0]
+    _near_best(pcfg, weights, prompt, res.token_ids, 0.04)
+    assert len(llm.engine.runner._graphs) == 2
+
+
 def test_entry_point_refuses_bad_requests(model_folders):
     from cuinfer_b200 import LLM, SamplingParams
 
