@@ -107,6 +107,9 @@ class ModelRunner:
         self._ring = _PinnedRing()
         self._arena: Optional[torch.Tensor] = None
         self._graphs: Dict[tuple, "DecodeGraph"] = {}        # (rows bucket, context class) -> graph
+        self._step_graphs: Dict[tuple, "StepGraph"] = {}     # shape of a prompt-sized step -> graph (a few, oldest dropped)
+        self._step_seen: Dict[tuple, int] = {}
+        self.step_graph_replays = 0
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -210,8 +213,10 @@ class ModelRunner:
                 raise StepError(f"request {rid!r} cannot take part in a decode step")
             seen.add(rid)
 
-    def build_context(self, entries: Sequence[StepEntry], table_stride: Optional[int] = None):
-        """Pack the batch, copy it to the device and return ``(StepContext, logits_indices tensor)``."""
+    def build_context(self, entries: Sequence[StepEntry], table_stride: Optional[int] = None,
+                      arena: Optional[torch.Tensor] = None):
+        """Pack the batch, copy it to the device and return ``(StepContext, logits_indices tensor)``.
+        ``arena``: the device buffer to copy into (a captured step's own); default: the runner's."""
         mgr = self.manager
         R = len(entries)
         lens = [len(e.tokens) for e in entries]
@@ -274,9 +279,14 @@ class ModelRunner:
                 t0 += lens[r]
             group_offsets.append((o_sm, o_bt))
 
-        if self._arena is None or self._arena.numel() < total:
-            self._arena = torch.empty(max(4096, 1 << (total - 1).bit_length()), dtype=torch.int32, device=self.device)
-        dev = self._arena[:total]
+        if arena is not None:
+            if arena.numel() < total:
+                raise StepError(f"the step needs {total} words of metadata, its captured arena holds {arena.numel()}")
+            dev = arena[:total]
+        else:
+            if self._arena is None or self._arena.numel() < total:
+                self._arena = torch.empty(max(4096, 1 << (total - 1).bit_length()), dtype=torch.int32, device=self.device)
+            dev = self._arena[:total]
         self.mark_device_begin()
         dev.copy_(pinned[:total], non_blocking=True)
         self._ring.mark(ring_idx)
@@ -302,17 +312,52 @@ class ModelRunner:
         """Run the batch and return float32 logits ``[sum(len(e.want)), vocab]`` in entry order (device tensor)."""
         self._validate(entries)
         self.storage.zero_slots(self.manager.take_newly_admitted())
-        ctx, want = self.build_context(entries)
-        stream = self.model.forward(ctx)
-        if want.numel():
-            logits = self.model.logits(stream, want)
+        graph = self._step_graph(entries)
+        if graph is not None:
+            logits = graph.run(entries)
         else:
-            logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+            ctx, want = self.build_context(entries)
+            stream = self.model.forward(ctx)
+            if want.numel():
+                logits = self.model.logits(stream, want)
+            else:
+                logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         for e in entries:
             self.manager.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
-        self.tokens_run += ctx.num_tokens
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
+
+    # ---- prompt-sized steps whose shape repeats, as CUDA graphs -------------------------------------------
+    # Launching the ~9 kernels of a layer one by one costs the host about as long as they run (each launch is a few
+    # microseconds of Python, a kernel of a 2048-token portion 5-50 us), so a step whose shape — the number of tokens
+    # and of wanted logits of every entry — has been seen before is captured once and replayed from then on.  Chunked
+    # prefill at the token budget and benchmarks repeat shapes; other steps run eagerly as before.
+    STEP_GRAPH_MIN_TOKENS = 256
+    STEP_GRAPH_MAX_ENTRIES = 16
+    STEP_GRAPH_LIMIT = 4
+
+    def _step_graph(self, entries: Sequence[StepEntry]) -> Optional["StepGraph"]:
+        if not self.config.enable_cuda_graph or len(entries) > self.STEP_GRAPH_MAX_ENTRIES:
+            return None
+        lens = tuple(len(e.tokens) for e in entries)
+        if sum(lens) < self.STEP_GRAPH_MIN_TOKENS:
+            return None
+        key = (lens, tuple(len(e.want) for e in entries))
+        graph = self._step_graphs.get(key)
+        if graph is not None:
+            return graph
+        if len(self._step_seen) > 4096:
+            self._step_seen.clear()
+        seen = self._step_seen.get(key, 0) + 1
+        self._step_seen[key] = seen
+        if seen < 2:
+            return None
+        while len(self._step_graphs) >= self.STEP_GRAPH_LIMIT:
+            self._step_graphs.pop(next(iter(self._step_graphs)))          # the oldest; its memory pool goes with it
+        graph = StepGraph(self, key)
+        self._step_graphs[key] = graph
+        return graph
 
     def mark_device_begin(self) -> None:
         if self.timing is not None:
@@ -534,3 +579,52 @@ class DecodeGraph:
         self.graph.replay()
         kernels.note_flagged_launch(replayed=True)      # the captured kernels have bounded waits that raise a flag
         return self.logits
+
+
+class StepGraph:
+    """A CUDA graph of one step of a fixed shape: the same numbers of tokens and of wanted logits per entry.
+
+    Positions, cache slots, block tables, token ids and the indices of the wanted rows are data in the graph's own
+    device arena (packed by ``ModelRunner.build_context`` as for an eager step and refreshed by one copy), so any
+    requests of these lengths at any positions replay it.  What shapes a launch — the attention kernels' tile counts —
+    depends on the query lengths only, which are the key.  The first use runs the step eagerly (that is its result)
+    and then records it; later uses replay.  The logits tensor is overwritten by the next replay.
+    """
+
+    def __init__(self, runner: "ModelRunner", key: tuple) -> None:
+        self._runner = weakref.ref(runner)
+        lens, wants = key
+        T, R, S, G = sum(lens), len(lens), sum(wants), len(runner.groups)
+        self.stride = (runner.max_model_len + runner.page_size - 1) // runner.page_size
+        total = 3 * T + (R + 1) + 2 * R + S + G * (T + R * self.stride)
+        self.arena = torch.empty(total, dtype=torch.int32, device=runner.device)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        from .. import kernels
+
+        runner = self._runner()
+        if runner is None:
+            raise RuntimeError("the engine of this step graph is gone")
+        ctx, want = runner.build_context(entries, table_stride=self.stride, arena=self.arena)
+        if self.graph is not None:
+            self.graph.replay()
+            kernels.note_flagged_launch(replayed=True)
+            runner.step_graph_replays += 1
+            return self.logits
+
+        def forward() -> torch.Tensor:
+            stream = runner.model.forward(ctx)
+            if want.numel():
+                return runner.model.logits(stream, want)
+            return torch.empty((0, runner.vocab_size), dtype=torch.float32, device=runner.device)
+
+        logits = forward()                       # this step's result; also creates what must exist before a capture
+        torch.cuda.synchronize(runner.device)
+        gc.collect()                             # see DecodeGraph.capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="relaxed"):
+            self.logits = forward()              # recorded, not run
+        self.graph = graph
+        return logits

@@ -104,7 +104,15 @@ def _check(rc: int, name: str) -> None:
         raise KernelError(f"{name} failed ({rc}): {msg.decode() if msg else 'no message'}")
 
 
+# torch's current stream as a raw pointer.  The private accessors skip the construction of a Stream object, which is
+# a microsecond and a half on every launch; without them the public call is used.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -120,6 +120,35 @@ def test_decode_graphs_per_context_class(model_folders):
     assert len(llm.engine.runner._graphs) == 2
 
 
+def test_repeated_prompt_shapes_replay_a_graph(model_folders):
+    """A prompt-sized step whose shape was seen before is captured and then replayed: four rounds of prompts of the
+    same lengths but other tokens, on other pages of the pool (pages that were given back are taken last), give the
+    plain implementation's tokens every time."""
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders["B"]
+    pcfg, weights = plain_qwen3.load_folder(folders["float32"])
+    llm = LLM(folders["float32"], dtype="float32", block_size=block, num_blocks=48, max_num_seqs=4,
+              max_num_scheduled_tokens=1024)
+    for round_ in range(4):
+        prompts = [random_tokens(cfg["vocab_size"], n, 300 + 10 * round_ + i) for i, n in enumerate([300, 270])]
+        out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+        for prompt, res in zip(prompts, out):
+            assert res.token_ids == plain_qwen3.greedy_generate(pcfg, weights, prompt, 5), round_
+    runner = llm.engine.runner
+    assert len(runner._step_graphs) == 1 and runner.step_graph_replays == 2
+    runner.manager.check()
+    # bfloat16 on the head-128 model: the tensor-core kernels inside the captured step
+    folders, cfg, block = model_folders["D"]
+    pcfg, weights = plain_qwen3.load_folder(folders["bfloat16"])
+    llm = LLM(folders["bfloat16"], dtype="bfloat16", block_size=block, num_blocks=64, max_num_seqs=2, max_num_scheduled_tokens=1024)
+    for round_ in range(3):
+        prompt = random_tokens(cfg["vocab_size"], 400, 500 + round_)
+        res = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))[0]
+        _near_best(pcfg, weights, prompt, res.token_ids, 0.04)
+    assert llm.engine.runner.step_graph_replays >= 1
+
+
 def test_entry_point_refuses_bad_requests(model_folders):
     from cuinfer_b200 import LLM, SamplingParams
 
