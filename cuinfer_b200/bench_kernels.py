@@ -103,13 +103,15 @@ def gemm(args) -> dict:
     def run(i):
         if args.impl == "tcgen05":
             kernels.gemm_tcgen05(x, w[i % copies], out)
+        elif args.impl == "wstream":
+            kernels.gemm_wstream(x, w[i % copies], out)
         elif args.impl == "cublas":
             torch.mm(x, w[i % copies].t(), out=out)
         else:
             matmul_nt(x, w[i % copies], out_dtype)
 
     ms = _time(run, args.iters)
-    if args.impl == "tcgen05":
+    if args.impl in ("tcgen05", "wstream"):
         kernels.check_error_flags()
     return {"kernel": f"matmul_nt[{args.impl}]", "M": M, "N": N, "K": K, "ms": round(ms, 4),
             "GBps": round((N * K + M * K + M * N) * 2 / ms / 1e6, 1), "TFLOPs": round(2.0 * M * N * K / ms / 1e9, 2)}
@@ -174,7 +176,7 @@ def main(argv=None) -> int:
     g.add_argument("--n", type=int, default=4096)
     g.add_argument("--k", type=int, default=1024)
     g.add_argument("--f32-out", action="store_true")
-    g.add_argument("--impl", default="auto", choices=["auto", "tcgen05", "cublas"])
+    g.add_argument("--impl", default="auto", choices=["auto", "tcgen05", "wstream", "cublas"])
     g.add_argument("--pdl", action="store_true", help="launch with programmatic dependent launch")
     g.add_argument("--copies", type=int, default=8)
     g.add_argument("--iters", type=int, default=20)

@@ -77,6 +77,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_attention_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
         "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P],
         "cib_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+        "cib_gemm_wstream": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
         "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
     }
@@ -90,6 +91,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.cib_gemm_tcgen05_supports.restype = _I
     lib.cib_attention_tcgen05_supports.argtypes = [_I, _I, _I, _I]
     lib.cib_attention_tcgen05_supports.restype = _I
+    lib.cib_gemm_wstream_supports.argtypes = [_I, _I, _I]
+    lib.cib_gemm_wstream_supports.restype = _I
     lib.cib_gemm_skinny_supports.argtypes = [_I, _I, _I, _I]
     lib.cib_gemm_skinny_supports.restype = _I
     lib.cib_paged_attention_prefill_supports.argtypes = [_I, _I, _I]
@@ -563,6 +566,33 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
         _cuda(seq_lens, "seq_lens", torch.int32), len(query_lens_host), tiles, num_q_heads, num_kv_heads, head_dim,
         float(scale), int(window), _error_flag(q.device).data_ptr(), _stream())
     _check(rc, "attention_tcgen05")
+    note_flagged_launch()
+    _count()
+
+
+def gemm_wstream_supports(M: int, N: int, K: int) -> bool:
+    return bool(library().cib_gemm_wstream_supports(M, N, K))
+
+
+def gemm_wstream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, silu_pair: bool = False) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T for up to 128 rows on tcgen05 tensor cores with the weights as the streamed
+    128-row operand (bfloat16 in, bfloat16 or float32 out).  ``silu_pair``: w holds N/2 gate rows then N/2 up rows and
+    out[M, N/2] = silu(gate) * up (bfloat16)."""
+    M, K = a.shape
+    N, K2 = w.shape
+    out_cols = N // 2 if silu_pair else N
+    if K != K2 or out.shape != (M, out_cols) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_wstream: a {list(a.shape)} {a.dtype}, w {list(w.shape)} {w.dtype}, out {list(out.shape)} do not fit")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_wstream: rows must be dense and out bfloat16 or float32")
+    if silu_pair and (N % 2 or out.dtype != torch.bfloat16):
+        raise KernelError("gemm_wstream: the gated epilogue needs an even N and a bfloat16 result")
+    epilogue = 2 if silu_pair else (1 if out.dtype == torch.float32 else 0)
+    rc = library().cib_gemm_wstream(
+        _cuda(a, "a", contiguous=False), a.stride(0), _cuda(w, "w", contiguous=False), w.stride(0),
+        _cuda(out, "out", contiguous=False), out.stride(0), epilogue, M, N, K, 1 if use_pdl else 0,
+        _error_flag(a.device).data_ptr(), _stream())
+    _check(rc, "gemm_wstream")
     note_flagged_launch()
     _count()
 

@@ -1,6 +1,7 @@
 """Choice of the bfloat16 matrix-product kernel for a given shape.
 
-* up to 16 rows (decode steps): the few-rows kernel (``gemm_skinny``), weights streamed once;
+* up to 16 rows (decode steps): the few-rows kernel (``gemm_skinny``), weights streamed once through registers; for K
+  above 4096 the weight-streaming tcgen05 kernel (``gemm_wstream``), which keeps more bytes in flight per SM;
 * 128 rows and more (prompt portions): the tcgen05 / TMA / TMEM kernel (``gemm_tcgen05``), with the SiLU gate in its
   epilogue for the gate/up projection;
 * in between, and for K that is not a multiple of 8: the library product (cuBLAS via ``torch.mm``; the reference
@@ -18,6 +19,9 @@ import os
 from .. import kernels
 
 TCGEN05_MIN_ROWS = 128
+FEW_ROWS = 16
+FUSED_NORM_MAX_K = 2048          # the norm prologue keeps 32-bit rows of all of K in shared memory: beyond this one CTA per SM
+FEW_ROWS_LONG_K = 4096           # above it the few-rows kernel is down to one CTA per SM (measured: 1.9 TB/s at K = 12288)
 _FORCE_CUBLAS = os.environ.get("CUINFER_B200_GEMM", "") == "cublas"
 
 
@@ -43,9 +47,14 @@ def bf16_matmul_nt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     """out[M, N] = x[M, K] @ weight[N, K]^T; x and weight bfloat16, out bfloat16 or float32."""
     M, K = x.shape
     N = weight.shape[0]
-    if M <= 16 and weight.is_contiguous() and kernels.gemm_skinny_supports(M, N, K):
-        kernels.gemm_skinny(weight, out, act=x)
-        return
+    if M <= FEW_ROWS and weight.stride(1) == 1 and x.stride(1) == 1:
+        long_k = K > FEW_ROWS_LONG_K and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and kernels.gemm_wstream_supports(M, N, K)
+        if not long_k and weight.is_contiguous() and kernels.gemm_skinny_supports(M, N, K):
+            kernels.gemm_skinny(weight, out, act=x)
+            return
+        if long_k:
+            kernels.gemm_wstream(x, weight, out)
+            return
     if takes_tcgen05(x, weight):
         kernels.gemm_tcgen05(x, weight, out)
         return

@@ -98,11 +98,21 @@ class Linear:
         if silu_pair and out_dtype != torch.bfloat16:
             return None
         out_cols = N // 2 if silu_pair else N
+        from . import gemm_dispatch
+        if K > gemm_dispatch.FEW_ROWS_LONG_K:
+            # long K: the weight-streaming kernel (no norm prologue; the gate is in its epilogue)
+            rows = x.materialize() if lazy else x
+            if (not silu_pair or rows.dtype != torch.bfloat16 or rows.stride(1) != 1 or rows.stride(0) % 8 or w.stride(0) % 8
+                    or not kernels.gemm_wstream_supports(M, N, K)):
+                return None
+            out = torch.empty((M, out_cols), dtype=torch.bfloat16, device=w.device)
+            kernels.gemm_wstream(rows, w, out, silu_pair=True)
+            return out
         if lazy and x._rows is None:
             from .norm import RMSNorm
             norm, stream = x.norm, x.stream
             if (type(norm) is RMSNorm and norm.weight is not None and stream.residual.is_contiguous()
-                    and kernels.gemm_skinny_supports(M, N, K, True)
+                    and K <= gemm_dispatch.FUSED_NORM_MAX_K and kernels.gemm_skinny_supports(M, N, K, True)
                     and (stream.pending is None or stream.pending.is_contiguous())):
                 out = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
                 has_delta = stream.pending is not None

@@ -157,6 +157,38 @@ def test_gemm_tcgen05_gated(M, I, K):
     assert torch.equal(wide[:, :I].cpu(), out.cpu()) and bool((wide[:, I:] == 7.0).all())
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 40, 64, 100, 128])
+@pytest.mark.parametrize("N, K", [(1024, 1024), (136, 72), (4096, 4096), (1000, 2048), (256, 12288)])
+@pytest.mark.parametrize("f32_out", [False, True])
+def test_gemm_wstream(M, N, K, f32_out):
+    """Weights as the streamed tensor-core operand: every row-count class, feature counts that end inside a tile,
+    K that ends inside a step, and shapes whose K is split over a cluster (few tiles, long K)."""
+    k = _k()
+    assert k.gemm_wstream_supports(M, N, K)
+    a, w = rand(M, K, seed=25, dtype=torch.bfloat16), rand(N, K, seed=26, scale=0.05, dtype=torch.bfloat16)
+    out = torch.full((M, N), 7.0, dtype=torch.float32 if f32_out else torch.bfloat16, device=DEV)
+    for _ in range(2):
+        k.gemm_wstream(a.to(DEV), w.to(DEV), out)
+        k.check_error_flags()
+    want = a.double() @ w.double().T
+    close(out, want, 2e-5 if f32_out else 6e-3)
+    assert not k.gemm_wstream_supports(129, N, K) and not k.gemm_wstream_supports(M, N, 20)
+
+
+@pytest.mark.parametrize("M", [3, 16, 33, 128])
+@pytest.mark.parametrize("I, K", [(3072, 1024), (200, 136), (64, 4096), (1000, 72)])
+def test_gemm_wstream_gated(M, I, K):
+    k = _k()
+    a = rand(M, K, seed=27, dtype=torch.bfloat16)
+    w = rand(2 * I, K, seed=28, scale=0.08, dtype=torch.bfloat16)
+    wide = torch.full((M, I + 8), 7.0, dtype=torch.bfloat16, device=DEV)
+    k.gemm_wstream(a.to(DEV), w.to(DEV), wide[:, :I], silu_pair=True)
+    k.check_error_flags()
+    y = a.double() @ w.double().T
+    close(wide[:, :I], torch.nn.functional.silu(y[:, :I]) * y[:, I:], 6e-3)
+    assert bool((wide[:, I:] == 7.0).all())
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N, K", [(1024, 1024), (48, 96), (1000, 2048), (3000, 72), (151936, 1024)])
 def test_gemm_skinny(M, N, K):
