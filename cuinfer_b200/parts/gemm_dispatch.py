@@ -3,12 +3,15 @@
 * up to 16 rows (decode steps): the few-rows kernel (``gemm_skinny``), weights streamed once through registers; for K
   above 4096 the weight-streaming tcgen05 kernel (``gemm_wstream``), which keeps more bytes in flight per SM;
 * 128 rows and more (prompt portions): the tcgen05 / TMA / TMEM kernel (``gemm_tcgen05``), with the SiLU gate in its
-  epilogue for the gate/up projection;
+  epilogue for the gate/up projection — where the product has at least ``TCGEN05_MIN_TILES`` output tiles of
+  128 x 128.  With fewer, every CTA walks the whole of K alone and the library, which splits K over more CTAs, measured
+  1.3 to 2.7 times faster (2048 x 1024 x 2048: 8.8 us against 14.9), so those go to cuBLAS;
 * in between, and for K that is not a multiple of 8: the library product (cuBLAS via ``torch.mm``; the reference
   calls cuBLAS for every projection, csrc/ops/projection.cu:32-44), or the FMA kernel for shapes cuBLAS's
   tensor-core paths do not take.
 
-``CUINFER_B200_GEMM=cublas`` sends every prompt-sized product to the library (for comparisons).
+``CUINFER_B200_GEMM=cublas`` sends every prompt-sized product to the library, ``CUINFER_B200_GEMM=tcgen05`` every one
+that the kernel takes to the kernel (for comparisons).
 """
 from __future__ import annotations
 
@@ -19,24 +22,32 @@ import os
 from .. import kernels
 
 TCGEN05_MIN_ROWS = 128
+TCGEN05_MIN_TILES = 296          # output tiles of 128 x 128 from which the tcgen05 kernel is chosen over the library
 FEW_ROWS = 16
 FUSED_NORM_MAX_K = 2048          # the norm prologue keeps 32-bit rows of all of K in shared memory: beyond this one CTA per SM
 FEW_ROWS_LONG_K = 4096           # above it the few-rows kernel is down to one CTA per SM (measured: 1.9 TB/s at K = 12288)
 _FORCE_CUBLAS = os.environ.get("CUINFER_B200_GEMM", "") == "cublas"
+_FORCE_TCGEN05 = os.environ.get("CUINFER_B200_GEMM", "") == "tcgen05"
 
 
-def takes_tcgen05(x: torch.Tensor, weight: torch.Tensor) -> bool:
+def takes_tcgen05(x: torch.Tensor, weight: torch.Tensor, fused: bool = False) -> bool:
+    """``fused``: the product carries an epilogue (the SiLU gate) that the library call would need another kernel for;
+    it stays on the tcgen05 kernel whatever its size."""
     M, K = x.shape
-    return (M >= TCGEN05_MIN_ROWS and not _FORCE_CUBLAS and x.stride(1) == 1 and weight.stride(1) == 1
-            and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
-            and kernels.gemm_tcgen05_supports(M, weight.shape[0], K))
+    N = weight.shape[0]
+    if not (M >= TCGEN05_MIN_ROWS and not _FORCE_CUBLAS and x.stride(1) == 1 and weight.stride(1) == 1
+            and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and kernels.gemm_tcgen05_supports(M, N, K)):
+        return False
+    if fused or _FORCE_TCGEN05 or K % 8 or N % 8:
+        return True
+    return -(-M // 128) * -(-N // 128) >= TCGEN05_MIN_TILES
 
 
 def bf16_gated_matmul_nt(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor | None:
     """silu(x gate^T) * (x up^T) for a weight of gate rows then up rows, in one tcgen05 kernel, when the shape is one
     it takes (prompt-sized, half of N a multiple of 8); None otherwise."""
     N = weight.shape[0]
-    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or N % 16 or not takes_tcgen05(x, weight):
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or N % 16 or not takes_tcgen05(x, weight, fused=True):
         return None
     out = torch.empty((x.shape[0], N // 2), dtype=torch.bfloat16, device=x.device)
     kernels.gemm_tcgen05(x, weight, out, silu_pair=True)
@@ -55,10 +66,11 @@ def bf16_matmul_nt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
         if long_k:
             kernels.gemm_wstream(x, weight, out)
             return
-    if takes_tcgen05(x, weight):
+    library_ok = K % 8 == 0 and N % 8 == 0 and x.is_contiguous() and weight.is_contiguous()
+    if takes_tcgen05(x, weight, fused=not library_ok):       # a product the library call cannot take stays on the kernel
         kernels.gemm_tcgen05(x, weight, out)
         return
-    if K % 8 == 0 and N % 8 == 0 and x.is_contiguous() and weight.is_contiguous():
+    if library_ok:
         if out.dtype == torch.bfloat16:
             torch.mm(x, weight.t(), out=out)
             return
