@@ -44,9 +44,10 @@ TINY_C = _cfg(num_hidden_layers=1, hidden_size=80, num_attention_heads=6, num_ke
               intermediate_size=176, vocab_size=517, rope_theta=500000.0, rms_norm_eps=3e-6,
               tie_word_embeddings=False, max_position_embeddings=1536)
 # head size 128 with two query heads per kv head: the shape that the tensor-core attention kernels and, from 128 rows
-# on, the tcgen05 projections take in bfloat16 (A, B and C run on the all-sizes kernels)
+# on, the tcgen05 projections take in bfloat16 (A, B and C run on the all-sizes kernels); the feed-forward is wider
+# than 4096, so that its down projection takes the weight-streaming kernel in decode steps
 TINY_D = _cfg(num_hidden_layers=2, hidden_size=192, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
-              intermediate_size=448, vocab_size=777, rope_theta=1000000.0, rms_norm_eps=1e-6,
+              intermediate_size=4224, vocab_size=777, rope_theta=1000000.0, rms_norm_eps=1e-6,
               tie_word_embeddings=True, max_position_embeddings=1024, eos_token_id=5)
 
 TINY = {"A": (TINY_A, dict(seed=0, std=0.05, gain_std=0.0, block_size=16)),
