@@ -216,7 +216,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               const int* __restrict__ seq_lens, int nq, int nkv, float scale_log2, int window,
                               int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
                               int* __restrict__ counters, const DecodeFuse f, const __grid_constant__ CUtensorMap kv_map,
-                              int* __restrict__ error_flag) {
+                              int* __restrict__ error_flag, const void* __restrict__ warm, unsigned long long warm_bytes) {
     static_assert(!(FUSED && TMA), "the folded-in step writes rows of the cp.async layout");
     extern __shared__ __align__(128) unsigned char smem_unaligned[];
     // TMA writes whole 1024-byte swizzle atoms: the rings then start on such a boundary
@@ -492,6 +492,10 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             }
         }
     }
+    // the stream of keys and values is over: what the kernel after this one reads first (the output projection's weights)
+    // can come into the L2 while the partial results are merged
+    if (threadIdx.x == 0)
+        warm_l2_share(warm, warm_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
     if (!TMA) cp_async_wait<0>();
     __syncthreads();     // all rings are free: reuse shared memory for the merge of the warps
 
@@ -601,7 +605,8 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                          int page_size, const int* block_table, int table_stride, const int* seq_lens,
                          int num_requests, int nq, int nkv, float scale, int window, int splits, float* part_o,
                          float* part_ml, int* counters, cudaStream_t stream, bool use_pdl = false,
-                         const DecodeFuse* fuse = nullptr, int* error_flag = nullptr) {
+                         const DecodeFuse* fuse = nullptr, int* error_flag = nullptr, const void* warm = nullptr,
+                         unsigned long long warm_bytes = 0) {
     const int g = nq / nkv;
     DecodeFuse f;
     if (fuse) f = *fuse;
@@ -644,7 +649,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     cudaError_t e = launch_pdl(kernel, grid, dim3(kDecWarps * 32), smem, stream, use_pdl,
                                (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                                (const __nv_bfloat16*)cache, num_pages, page_size, block_table, table_stride, seq_lens, nq,
-                               nkv, scale_log2, window, splits, part_o, part_ml, counters, f, kv_map, error_flag);
+                               nkv, scale_log2, window, splits, part_o, part_ml, counters, f, kv_map, error_flag, warm, warm_bytes);
     if (e != cudaSuccess) {
         set_error("paged_attention_decode: launch failed: %s", cudaGetErrorString(e));
         return -2;
@@ -670,11 +675,13 @@ extern "C" long long cib_paged_attention_decode_scratch_floats(int num_requests,
 // splits == 1); `counters` holds num_requests * nkv ints that are zero before the first call (the kernel leaves
 // them zero).  `error_flag` (one zero int in device memory, or null) lets the kernel fetch the cache through TMA
 // where the geometry allows it: a copy that does not land in time sets the flag instead of hanging the kernel.
+// warm / warm_bytes: memory that the kernel after this one reads first, or null: fetched into the L2 at the kernel's end.
 extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* cache,
                                           int num_pages, int page_size, const int* block_table, int table_stride,
                                           const int* seq_lens, int num_requests, int nq, int nkv, int head_dim,
                                           float scale, int window, int splits, float* scratch, int* counters,
-                                          int use_pdl, int* error_flag, cudaStream_t stream) {
+                                          int use_pdl, int* error_flag, const void* warm, long long warm_bytes,
+                                          cudaStream_t stream) {
     CIB_REQUIRE(cib_paged_attention_decode_supports(head_dim, nq, nkv),
                 "paged_attention_decode: head_dim %d with %d/%d heads is not taken by this kernel (64, 128 or 256; at most 16 query heads per kv head)",
                 head_dim, nq, nkv);
@@ -686,10 +693,12 @@ extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out
     if (num_requests == 0) return 0;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_requests * nq * splits * head_dim : nullptr;
+    if (((uintptr_t)warm % 16) != 0 || warm_bytes <= 0) { warm = nullptr; warm_bytes = 0; }
+    const unsigned long long wb = (unsigned long long)warm_bytes;
     switch (head_dim) {
-        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag);
-        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag);
-        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag);
+        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag, warm, wb);
+        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag, warm, wb);
+        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag, warm, wb);
     }
     return -1;
 }

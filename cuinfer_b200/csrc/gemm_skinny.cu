@@ -35,6 +35,7 @@ struct SkinnyArgs {
     void* out; int ldo; int M;
     int up_offset;                                           // kSiluPair: first row of the "up" half
     int act_stride;                                          // shared-memory row stride in elements
+    const void* warm; unsigned long long warm_bytes;         // the weights of the kernel after this one (or null): fetched into L2
 };
 
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
@@ -89,6 +90,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
         }
     };
     load_chunk(waA, wbA, step_begin);   // weights do not depend on the kernel before this one
+    if (tid == 0) warm_l2_share(a.warm, a.warm_bytes, blockIdx.x, gridDim.x);
     griddep_launch();
     griddep_wait();                     // from here on the previous kernel's results may be read
 
@@ -385,10 +387,11 @@ extern "C" int cib_gemm_skinny_supports(int M, int N, int K, int with_norm) {
 // RMSNorm(res_in + pending) * norm_w computed in the kernel, and res_out (if not null) receives res_in + pending.
 // epilogue: 0 = bfloat16 out[M, N]; 1 = float32 out[M, N]; 2 = rows [0, up_offset) are gates and rows
 // [up_offset, N) the matching ups: out[M, up_offset] = silu(gate) * up in bfloat16.
+// warm / warm_bytes: memory that the kernel after this one reads first (its weights), or null: fetched into the L2 meanwhile.
 extern "C" int cib_gemm_skinny(const void* w, int ldw, int N, int K, const void* act, int lda, const float* res_in,
                                const void* pending, int pending_dtype, const void* norm_w, int norm_w_dtype, float eps,
                                float* res_out, void* out, int ldo, int M, int epilogue, int up_offset, int use_pdl,
-                               cudaStream_t stream) {
+                               const void* warm, long long warm_bytes, cudaStream_t stream) {
     CIB_REQUIRE(cib_gemm_skinny_supports(M, N, K, res_in != nullptr), "gemm_skinny: M=%d N=%d K=%d is not taken by this kernel (M <= 16, K a multiple of 8)", M, N, K);
     CIB_REQUIRE(ldw >= K && ldw % 8 == 0 && ((uintptr_t)w % 16) == 0, "gemm_skinny: weight rows must be 16-byte aligned");
     CIB_REQUIRE((act != nullptr) != (res_in != nullptr), "gemm_skinny: give plain activations or a residual to normalise");
@@ -403,6 +406,8 @@ extern "C" int cib_gemm_skinny(const void* w, int ldw, int N, int K, const void*
     a.res_in = res_in; a.pending = pending; a.pending_bf16 = pending_dtype == kBF16;
     a.norm_w = AnyVec{norm_w, norm_w_dtype == kBF16}; a.eps = eps; a.res_out = res_out;
     a.out = out; a.ldo = ldo; a.M = M; a.up_offset = up_offset; a.act_stride = 0;
+    a.warm = ((uintptr_t)warm % 16) == 0 && warm_bytes > 0 ? warm : nullptr;
+    a.warm_bytes = a.warm ? (unsigned long long)warm_bytes : 0;
     if (M <= 8) return dispatch_skinny<1>(a, epilogue, use_pdl, stream);
     return dispatch_skinny<2>(a, epilogue, use_pdl, stream);
 }

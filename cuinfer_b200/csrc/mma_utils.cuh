@@ -43,6 +43,21 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Ask for this CTA's share of `bytes` at `ptr` (16-byte aligned) to be fetched into the L2: one bulk prefetch by one
+// thread.  A decode step is a chain of short kernels that each wait about two microseconds for their first weights
+// to come from memory; a kernel that names the weights of the kernel after it lets that wait pass while it runs.
+__device__ __forceinline__ void warm_l2_share(const void* ptr, unsigned long long bytes, unsigned cta, unsigned ctas) {
+    if (ptr == nullptr || bytes == 0) return;
+    unsigned long long per = ((bytes + ctas - 1) / ctas + 15) & ~15ull;
+    if (per > (1ull << 20)) per = 1ull << 20;                  // a bounded request; what is left is fetched when it is read
+    const unsigned long long off = (unsigned long long)cta * per;
+    if (off >= bytes) return;
+    unsigned long long n = bytes - off < per ? bytes - off : per;
+    n &= ~15ull;
+    if (n == 0) return;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const unsigned char*>(ptr) + off), "r"((unsigned)n) : "memory");
+}
+
 // Launch with or without the programmatic-dependent-launch attribute.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -70,12 +70,12 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_silu_mul": [_P, _P, _I, _I, _I, _P],
         "cib_qk_norm_rope_kv_write": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
-        "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _P],
+        "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _P, ctypes.c_longlong, _P],
         "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
         "cib_paged_attention_decode_fused": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I,
                                              _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P],
         "cib_attention_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
-        "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P],
+        "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "cib_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "cib_gemm_wstream": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
@@ -300,11 +300,12 @@ DECODE_TMA_MIN_KEYS = 1536      # keys per CTA from which the TMA path of the de
 
 def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                            seq_lens: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                           window: int, splits: int, tma: bool | None = None) -> None:
+                           window: int, splits: int, tma: bool | None = None, warm: torch.Tensor | None = None) -> None:
     """bfloat16 attention of one query token per request (``q[r, :nq*d]``) over the paged cache, the keys of
     every (request, kv head) split over ``splits`` CTAs.  Allocates the partial-result scratch with torch.
     ``tma``: let the kernel fetch the cache through TMA where the geometry allows it (default: yes).  That path
-    streams faster but starts slower, so callers that know the keys per CTA pass False for short streams."""
+    streams faster but starts slower, so callers that know the keys per CTA pass False for short streams.
+    ``warm``: a tensor that the kernel after this one reads first; fetched into the L2 when the stream of keys ends."""
     R = q.shape[0]
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("paged_attention_decode: bfloat16 only")
@@ -331,7 +332,9 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
         block_table.stride(0), _cuda(seq_lens, "seq_lens", torch.int32), R, num_q_heads, num_kv_heads, head_dim,
         float(scale), int(window), int(splits), scratch.data_ptr() if scratch is not None else None,
         counters.data_ptr() if counters is not None else None, 1 if use_pdl else 0,
-        _error_flag(q.device).data_ptr() if decode_tma and tma is not False else None, _stream())
+        _error_flag(q.device).data_ptr() if decode_tma and tma is not False else None,
+        warm.data_ptr() if warm is not None else None, warm.numel() * warm.element_size() if warm is not None else 0,
+        _stream())
     _check(rc, "paged_attention_decode")
     note_flagged_launch()
     _count()
@@ -449,8 +452,9 @@ def gemm_skinny_supports(M: int, N: int, K: int, with_norm: bool = False) -> boo
 def gemm_skinny(w: torch.Tensor, out: torch.Tensor, *, act: torch.Tensor | None = None,
                 residual: torch.Tensor | None = None, pending: torch.Tensor | None = None,
                 norm_weight: torch.Tensor | None = None, eps: float = 0.0, residual_out: torch.Tensor | None = None,
-                silu_pair: bool = False) -> None:
-    """out = act @ w^T for at most 16 rows, bfloat16 weights.
+                silu_pair: bool = False, warm: torch.Tensor | None = None) -> None:
+    """out = act @ w^T for at most 16 rows, bfloat16 weights.  ``warm``: a tensor that the kernel after this one
+    reads first (its weights); the kernel asks for it to be fetched into the L2 while it runs.
 
     Either ``act`` [M, K] is given, or ``residual`` (float32 [M, K]) with optional ``pending``: then the rows are
     RMSNorm(residual + pending) * norm_weight, computed in the kernel, and ``residual_out`` (another buffer)
@@ -493,7 +497,9 @@ def gemm_skinny(w: torch.Tensor, out: torch.Tensor, *, act: torch.Tensor | None 
         _cuda(norm_weight, "norm_weight") if norm_weight is not None else None,
         _code(norm_weight, "norm_weight") if norm_weight is not None else 0, float(eps),
         _cuda(residual_out, "residual_out") if residual_out is not None else None,
-        _cuda(out, "out", contiguous=False), out.stride(0), M, epi, N // 2 if silu_pair else 0, 1 if use_pdl else 0, _stream())
+        _cuda(out, "out", contiguous=False), out.stride(0), M, epi, N // 2 if silu_pair else 0, 1 if use_pdl else 0,
+        warm.data_ptr() if warm is not None else None, warm.numel() * warm.element_size() if warm is not None else 0,
+        _stream())
     _check(rc, "gemm_skinny")
     _count()
 

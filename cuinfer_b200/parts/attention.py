@@ -84,6 +84,12 @@ class PagedAttention(Mixer):
                 self.k_norm_weight = self.k_norm_weight.float()
         self.position.load(store)
 
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return self.qkv.weight
+
+    def warm_after(self, weight: Optional[torch.Tensor]) -> None:
+        self.o.warm_next = weight
+
     def cache_need(self) -> Optional[PagedCacheNeed]:
         return PagedCacheNeed(self.num_kv_heads, self.head_dim, self.window or None)
 
@@ -108,5 +114,5 @@ class PagedAttention(Mixer):
             kv.cache if kv.writes else None, self.num_heads, self.num_kv_heads, self.head_dim)
         out = torch.empty((qkv.shape[0], self.q_size), dtype=qkv.dtype, device=qkv.device)
         attention_dispatch.paged_attention(qkv, out, kv, ctx, self.num_heads, self.num_kv_heads, self.head_dim,
-                                           self.scale, self.window)
+                                           self.scale, self.window, warm=self.o.weight)
         return self.o.forward(out)

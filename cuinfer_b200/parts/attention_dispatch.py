@@ -20,7 +20,9 @@ _FORCE_MMA = os.environ.get("CUINFER_B200_ATTENTION", "") == "mma"
 
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepContext, num_heads: int,
-                    num_kv_heads: int, head_dim: int, scale: float, window: int) -> None:
+                    num_kv_heads: int, head_dim: int, scale: float, window: int, warm: torch.Tensor | None = None) -> None:
+    """``warm``: what the step reads right after the attention (the output projection's weight); the decode kernel
+    asks for it to be fetched into the L2 when its stream of keys ends."""
     if (qkv.dtype == torch.bfloat16 and ctx.decode_only
             and kernels.paged_attention_decode_supports(head_dim, num_heads, num_kv_heads)):
         longest = max(1, ctx.max_seq_len)
@@ -28,7 +30,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: Step
         # the TMA path of the kernel streams faster but takes longer to start: only for long streams per CTA
         tma = -(-longest // splits) >= kernels.DECODE_TMA_MIN_KEYS
         kernels.paged_attention_decode(qkv, out, kv.cache, kv.group.block_table, ctx.seq_lens, num_heads,
-                                       num_kv_heads, head_dim, scale, window, splits, tma=tma)
+                                       num_kv_heads, head_dim, scale, window, splits, tma=tma, warm=warm)
         return
     if qkv.dtype == torch.bfloat16 and not _FORCE_MMA and kernels.attention_tcgen05_supports(
             head_dim, num_heads, num_kv_heads, kv.group.page_size) and out.stride(0) % 8 == 0 and qkv.stride(0) % 8 == 0:

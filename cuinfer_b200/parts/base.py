@@ -88,6 +88,16 @@ class Part:
     def load(self, store) -> None:  # store: cuinfer_b200.weights.WeightStore
         pass
 
+    # A decode step is a chain of short kernels, each of which waits for its first weights to come from memory.  A
+    # part may name the weight it reads first, and be told which weight the step reads right after it: its last
+    # kernel can then ask for that weight to be fetched into the L2 while it runs.  Both are hints; the defaults do
+    # nothing.  The model wires them after loading, along the order in which its layers run.
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return None
+
+    def warm_after(self, weight: Optional[torch.Tensor]) -> None:
+        pass
+
 
 class Norm(Part):
     def add_norm(self, stream: ResidualStream) -> torch.Tensor:
@@ -134,3 +144,11 @@ class Block:
 
     def forward(self, stream: ResidualStream, ctx: StepContext, run: int) -> None:
         raise NotImplementedError
+
+    # hints for the L2 (see Part): the weight the layer reads first, and the weight that follows the layer
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return self.mixer.first_weight()
+
+    def warm_after(self, weight: Optional[torch.Tensor]) -> None:
+        self.mixer.warm_after(self.feed_forward.first_weight())
+        self.feed_forward.warm_after(weight)

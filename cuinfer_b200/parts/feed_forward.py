@@ -6,7 +6,7 @@ csrc/ops/swiglu.cu:23-32).  Spec: ``PartSpec("swiglu", intermediate_size=I)``.
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -36,6 +36,13 @@ class SwiGLU(FeedForward):
     def load(self, store) -> None:
         self.gate_up.load(store)
         self.down.load(store)
+        self.gate_up.warm_next = self.down.weight
+
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return self.gate_up.weight
+
+    def warm_after(self, weight: Optional[torch.Tensor]) -> None:
+        self.down.warm_next = weight
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = self.gate_up.forward(x, silu_pair=True)       # silu(gate) * up, fused where the kernel allows

@@ -45,6 +45,7 @@ class Linear:
         self.in_features = in_features
         self.dtype = dtype
         self.weight: Optional[torch.Tensor] = None
+        self.warm_next: Optional[torch.Tensor] = None     # what the step reads right after this projection (a hint for the L2)
 
     def tensors(self) -> List[TensorSpec]:
         return [TensorSpec(n, (o, self.in_features)) for n, o in zip(self.names, self.out_features)]
@@ -117,15 +118,14 @@ class Linear:
                 out = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
                 has_delta = stream.pending is not None
                 kernels.gemm_skinny(w, out, residual=stream.residual, pending=stream.pending, norm_weight=norm.weight,
-                                    eps=norm.eps, residual_out=stream.spare() if has_delta else None, silu_pair=silu_pair)
+                                    eps=norm.eps, residual_out=stream.spare() if has_delta else None, silu_pair=silu_pair,
+                                    warm=self.warm_next)
                 if has_delta:
                     stream.swap()
                 return out
         rows = x.materialize() if lazy else x
         if rows.dtype != torch.bfloat16 or rows.stride(1) != 1 or not kernels.gemm_skinny_supports(M, N, K, False):
             return None
-        if not silu_pair and not lazy:
-            return None          # the plain case goes through matmul_nt, which picks the same kernel
         out = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
-        kernels.gemm_skinny(w, out, act=rows, silu_pair=silu_pair)
+        kernels.gemm_skinny(w, out, act=rows, silu_pair=silu_pair, warm=self.warm_next)
         return out

@@ -87,6 +87,11 @@ class DecoderModel:
         else:
             self.lm_head.load(store)
         self._bad_id_flag = torch.zeros(1, dtype=torch.int32, device=store.device)
+        # hints for the L2 along the order in which the layers run: every layer is told which weight follows it
+        runs = self.runs()
+        for i, (_run, layer) in enumerate(runs):
+            follower = self.blocks[runs[i + 1][1]].first_weight() if i + 1 < len(runs) else None
+            self.blocks[layer].warm_after(follower)
 
     # ---- what the layers keep between steps ----------------------------------------------------
     def runs(self) -> List[Tuple[int, int]]:
