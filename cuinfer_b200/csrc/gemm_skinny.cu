@@ -36,6 +36,7 @@ struct SkinnyArgs {
     int up_offset;                                           // kSiluPair: first row of the "up" half
     int act_stride;                                          // shared-memory row stride in elements
     const void* warm; unsigned long long warm_bytes;         // the weights of the kernel after this one (or null): fetched into L2
+    int norm_w_offset;                                       // byte offset of the norm gains' copy in shared memory
 };
 
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
@@ -91,8 +92,14 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     };
     load_chunk(waA, wbA, step_begin);   // weights do not depend on the kernel before this one
     if (tid == 0) warm_l2_share(a.warm, a.warm_bytes, blockIdx.x, gridDim.x);
+    // neither do the norm's gains: they wait in shared memory (read from global memory in the second pass of the norm,
+    // eight dependent round trips per row, they were a third of this kernel's time)
+    float* s_nw = reinterpret_cast<float*>(smem_raw + a.norm_w_offset);
+    if (a.res_in != nullptr)
+        for (int k = tid; k < a.K; k += kSkWarps * 32) s_nw[k] = a.norm_w[k];
     griddep_launch();
     griddep_wait();                     // from here on the previous kernel's results may be read
+    if (a.res_in != nullptr) __syncthreads();      // the gains' copy is complete
 
     // ---- activations -> shared memory (bfloat16 rows, padded), optionally normalised on the way ----
     const int rows_pad = MT * 8;
@@ -155,8 +162,9 @@ skinny_gemm_kernel(const SkinnyArgs a) {
             for (int k = lane * 4; k < a.K; k += 128) {
                 float4 x = row < a.M ? *reinterpret_cast<const float4*>(s_x + (size_t)row * a.K + k)
                                      : make_float4(0.f, 0.f, 0.f, 0.f);
-                const float n0 = x.x * factor * a.norm_w[k], n1 = x.y * factor * a.norm_w[k + 1];
-                const float n2 = x.z * factor * a.norm_w[k + 2], n3 = x.w * factor * a.norm_w[k + 3];
+                const float4 gw = *reinterpret_cast<const float4*>(s_nw + k);
+                const float n0 = x.x * factor * gw.x, n1 = x.y * factor * gw.y;
+                const float n2 = x.z * factor * gw.z, n3 = x.w * factor * gw.w;
                 uint2 pk;
                 pk.x = pack_bf16(n0, n1);
                 pk.y = pack_bf16(n2, n3);
@@ -168,11 +176,27 @@ skinny_gemm_kernel(const SkinnyArgs a) {
         const int c_begin = CS > 1 ? min(a.K / 8, crank * KS * steps_per * 4) : 0;
         const int c_end = CS > 1 ? min(a.K / 8, (crank + 1) * KS * steps_per * 4) : a.K / 8;
         const int chunks = c_end - c_begin;
-        for (int idx = tid; idx < rows_pad * chunks; idx += kSkWarps * 32) {
-            const int row = idx / chunks, c = c_begin + idx % chunks;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (row < a.M) v = *reinterpret_cast<const uint4*>(a.act + (size_t)row * a.lda + c * 8);
-            *reinterpret_cast<uint4*>(s_act + (size_t)row * a.act_stride + c * 8) = v;
+        // four loads in flight per thread: one after the other they cost a round trip to the L2 each
+        const int total = rows_pad * chunks;
+        for (int base = tid; base < total; base += kSkWarps * 32 * 4) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = base + u * kSkWarps * 32;
+                v[u] = make_uint4(0, 0, 0, 0);
+                if (idx < total) {
+                    const int row = idx / chunks, c = c_begin + idx % chunks;
+                    if (row < a.M) v[u] = *reinterpret_cast<const uint4*>(a.act + (size_t)row * a.lda + c * 8);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = base + u * kSkWarps * 32;
+                if (idx < total) {
+                    const int row = idx / chunks, c = c_begin + idx % chunks;
+                    *reinterpret_cast<uint4*>(s_act + (size_t)row * a.act_stride + c * 8) = v[u];
+                }
+            }
         }
     }
     __syncthreads();
@@ -299,6 +323,9 @@ static int launch_skinny(SkinnyArgs& a, int grid, int use_pdl, cudaStream_t stre
     size_t red_bytes = (size_t)(KS + CS + 1) * RT * 16 * MT * 8 * 4;
     size_t smem = act_bytes + (norm_bytes > red_bytes ? norm_bytes : red_bytes);
     if (smem < red_bytes) smem = red_bytes;
+    smem = (smem + 15) & ~size_t(15);
+    a.norm_w_offset = (int)smem;
+    if (a.res_in) smem += (size_t)a.K * 4;
     CIB_REQUIRE(smem <= 200 * 1024, "gemm_skinny: %d rows x K=%d need %zu bytes of shared memory", a.M, a.K, smem);
     auto kernel = skinny_gemm_kernel<MT, RT, KS, EPI, CS>;
     static bool configured = false;
@@ -348,10 +375,11 @@ static int dispatch_skinny(SkinnyArgs& a, int epilogue, int use_pdl, cudaStream_
     // As few 16-row tiles per CTA as keep the launch within one round of CTAs (two fit on each of the 148 SMs);
     // the warps that are not needed for rows split K instead.
     const int tiles = (a.N + 15) / 16;
-    if (a.res_in == nullptr && tiles <= 148 && a.K >= 3072) {
+    if (a.res_in == nullptr && tiles <= 148 && a.K >= 2048) {
         // few output features and a long K: four CTAs of a cluster share each tile so that most SMs stream
-        // (a cluster launch costs about a microsecond more, so shorter K stays with one CTA per tile; with more
-        // tiles than SMs the split measured slower)
+        // (a cluster launch costs about a microsecond more, so K below 2048 stays with one CTA per tile; with more
+        // tiles than SMs the split measured slower).  At K = 2048 and 64 tiles the split turned a 6.6 us launch, whose
+        // warps fetched their second chunk of weights after the wait, into one whose weights are all asked for before it.
         if (epilogue == kStoreF32) return launch_skinny<MT, 1, 8, kStoreF32, 4>(a, tiles, use_pdl, stream);
         return launch_skinny<MT, 1, 8, kStoreBf16, 4>(a, tiles, use_pdl, stream);
     }
@@ -379,7 +407,7 @@ using namespace cib;
 extern "C" int cib_gemm_skinny_supports(int M, int N, int K, int with_norm) {
     if (!(M >= 1 && M <= 16 && N >= 1 && K >= 32 && K % 8 == 0)) return 0;
     const size_t rows = M <= 8 ? 8 : 16;
-    const size_t bytes = rows * (K + 64) * 2 + (with_norm ? rows * K * 4 : (size_t)kSkWarps * 16 * rows * 4);
+    const size_t bytes = rows * (K + 64) * 2 + (with_norm ? rows * K * 4 + (size_t)K * 4 + 16 : (size_t)kSkWarps * 16 * rows * 4);
     return bytes <= 200 * 1024 && (!with_norm || K % 4 == 0);
 }
 
