@@ -69,7 +69,7 @@ class EngineCore:
             self.stats["prefill_tokens" if s.is_prefill else "decode_tokens"] += len(s.tokens)
         wanted = [s for s in scheduled if s.needs_sampling]
         if len(wanted) == len(entries) and self.runner.can_use_graph(entries):
-            logits = self.runner.decode_step(entries)
+            logits = self.runner.decode_step(entries, trusted=True)
         else:
             logits = self.runner.step(entries)
         if not wanted:

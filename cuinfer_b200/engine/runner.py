@@ -394,10 +394,13 @@ class ModelRunner:
             self._graphs[(bucket, context)] = graph
         return graph
 
-    def decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def decode_step(self, entries: Sequence[StepEntry], trusted: bool = False) -> torch.Tensor:
         """One decode step (every entry brings one token and wants its logits) by graph replay.
-        Returns float32 logits ``[len(entries), vocab]``; the tensor is overwritten by the next decode step."""
-        self._validate_decode(entries)
+        Returns float32 logits ``[len(entries), vocab]``; the tensor is overwritten by the next decode step.
+        ``trusted``: the entries come from this package's scheduler, which has reserved their pages and sampled their
+        tokens itself; the per-entry checks are skipped."""
+        if not trusted:
+            self._validate_decode(entries)
         self.storage.zero_slots(self.manager.take_newly_admitted())
         mgr = self.manager
         starts = [mgr.num_tokens(e.request_id) for e in entries]
