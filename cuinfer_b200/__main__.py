@@ -45,6 +45,8 @@ def main(argv=None) -> int:
     g.add_argument("--max-num-scheduled-tokens", type=int, default=8192)
     g.add_argument("--max-num-seqs", type=int, default=256)
     g.add_argument("--disable-cuda-graph", action="store_true")
+    g.add_argument("--disable-run-ahead", action="store_true",
+                   help="wait for a decode step's tokens before launching the next one")
     args = parser.parse_args(argv)
 
     from .config import ConfigError, EngineConfig
@@ -59,7 +61,7 @@ def main(argv=None) -> int:
     try:
         options = dict(gpu_memory_utilization=args.gpu_memory_utilization, block_size=args.block_size,
                        max_num_scheduled_tokens=args.max_num_scheduled_tokens, max_num_seqs=args.max_num_seqs,
-                       enable_cuda_graph=not args.disable_cuda_graph, dtype=args.dtype, num_blocks=args.num_blocks,
+                       enable_cuda_graph=not args.disable_cuda_graph, decode_run_ahead=not args.disable_run_ahead, dtype=args.dtype, num_blocks=args.num_blocks,
                        seed=args.seed)
         EngineConfig(model_path=args.model or "", **options)
         params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,

@@ -31,7 +31,7 @@ class LLM:
     def __init__(self, model: str, **engine_options) -> None:
         """``model``: a folder with config.json and model.safetensors.  ``engine_options`` are the fields of
         :class:`EngineConfig` (gpu_memory_utilization, block_size, max_num_scheduled_tokens, max_num_seqs,
-        enable_cuda_graph, dtype, num_blocks, seed, device)."""
+        enable_cuda_graph, decode_run_ahead, dtype, num_blocks, seed, device)."""
         self.config = EngineConfig(model_path=model, **engine_options)
         self.engine = EngineCore(self.config)
         self._counter = 0

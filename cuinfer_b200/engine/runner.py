@@ -394,18 +394,20 @@ class ModelRunner:
             self._graphs[(bucket, context)] = graph
         return graph
 
-    def decode_step(self, entries: Sequence[StepEntry], trusted: bool = False) -> torch.Tensor:
+    def decode_step(self, entries: Sequence[StepEntry], trusted: bool = False,
+                    token_ids_device: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One decode step (every entry brings one token and wants its logits) by graph replay.
         Returns float32 logits ``[len(entries), vocab]``; the tensor is overwritten by the next decode step.
         ``trusted``: the entries come from this package's scheduler, which has reserved their pages and sampled their
-        tokens itself; the per-entry checks are skipped."""
+        tokens itself; the per-entry checks are skipped.  ``token_ids_device``: the step's input ids, one per entry, as
+        an int32 tensor on the device (the sampler's output of the step before); the entries' own ids are then ignored."""
         if not trusted:
             self._validate_decode(entries)
         self.storage.zero_slots(self.manager.take_newly_admitted())
         mgr = self.manager
         starts = [mgr.num_tokens(e.request_id) for e in entries]
         graph = self.decode_graph(len(entries), max(starts) + 1)
-        graph.upload(entries, starts)
+        graph.upload(entries, starts, token_ids_device)
         logits = graph.replay()
         for e in entries:
             self.manager.commit(e.request_id, 1)
@@ -504,7 +506,8 @@ class DecodeGraph:
         stream = self.runner.model.forward(self.ctx)
         return self.runner.model.logits(stream, self._dev("want"))
 
-    def upload(self, entries: Sequence[StepEntry], starts: Optional[List[int]] = None) -> None:
+    def upload(self, entries: Sequence[StepEntry], starts: Optional[List[int]] = None,
+               token_ids_device: Optional[torch.Tensor] = None) -> None:
         r = self.runner
         mgr = r.manager
         i = self.turn
@@ -559,6 +562,8 @@ class DecodeGraph:
         if self.events[i] is None:
             self.events[i] = torch.cuda.Event()
         self.events[i].record()
+        if token_ids_device is not None:
+            self._dev("tok")[:n].copy_(token_ids_device[:n], non_blocking=True)
 
     def capture(self) -> None:
         from .. import kernels

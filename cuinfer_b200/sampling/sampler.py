@@ -39,10 +39,27 @@ class Sampler:
     def __init__(self, seed: int, device: torch.device, max_rows: int) -> None:
         self.seed = seed
         self.device = device
-        self._host = torch.empty((max(1, max_rows), 4), dtype=torch.float32, pin_memory=True)
+        # the engine launches a step before it has waited for the one before: the options of a step are packed into a
+        # pinned buffer of their own turn, reused only after the copy that read it has run
+        self._hosts = [torch.empty((max(1, max_rows), 4), dtype=torch.float32, pin_memory=True) for _ in range(3)]
+        self._copied: List[torch.cuda.Event | None] = [None, None, None]
+        self._turn = 0
+        self._host = self._hosts[0]
         self._dev = torch.empty((max(1, max_rows), 4), dtype=torch.float32, device=device)
         self._ids = torch.empty(max(1, max_rows), dtype=torch.int32, device=device)
         self._greedy_rows = 0          # leading rows of the device buffer that hold plain argmax options
+
+    def _next_host(self) -> None:
+        self._turn = (self._turn + 1) % len(self._hosts)
+        if self._copied[self._turn] is not None:
+            self._copied[self._turn].synchronize()
+        self._host = self._hosts[self._turn]
+
+    def _upload(self, rows: int) -> None:
+        self._dev[:rows].copy_(self._host[:rows], non_blocking=True)
+        event = self._copied[self._turn] or torch.cuda.Event()
+        event.record()
+        self._copied[self._turn] = event
 
     def pack(self, params: Sequence[SamplingParams], request_keys: Sequence[int], output_indices: Sequence[int]) -> int:
         rows = len(params)
@@ -64,12 +81,14 @@ class Sampler:
         if all(p.greedy for p in params):
             # argmax rows need no uniform number: the packed rows on the device stay valid from step to step
             if self._greedy_rows < rows:
+                self._next_host()
                 self.pack([_GREEDY] * rows, [0] * rows, [0] * rows)
-                self._dev[:rows].copy_(self._host[:rows], non_blocking=True)
+                self._upload(rows)
                 self._greedy_rows = rows
         else:
+            self._next_host()
             self.pack(params, request_keys, output_indices)
-            self._dev[:rows].copy_(self._host[:rows], non_blocking=True)
+            self._upload(rows)
             self._greedy_rows = 0
         out = self._ids[:rows]
         kernels.sample(logits, self._dev[:rows], out)

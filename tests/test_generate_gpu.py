@@ -97,6 +97,57 @@ def test_eos_stops_and_is_returned(model_folders):
         assert go_on.finish_reason == "length" and go_on.token_ids == free_run
 
 
+def test_run_ahead_gives_the_same_outputs(model_folders):
+    """Launching the next decode step before the ids of the one in flight have been read changes nothing: requests of
+    different lengths and budgets (so that the run-ahead stops and starts), one that stops at an end-of-sequence token
+    while its next step is already in flight, one that is aborted in flight, temperature sampling with a seed."""
+    import shutil, tempfile
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders["B"]
+    folder = folders["float32"]
+    pcfg, weights = plain_qwen3.load_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, 400 + i) for i, n in enumerate([9, 40, 3, 77, 21])]
+    free = plain_qwen3.greedy_generate(pcfg, weights, prompts[1], 10)
+    with tempfile.TemporaryDirectory() as tmp:
+        shutil.copytree(folder, tmp, dirs_exist_ok=True)
+        raw = json.load(open(os.path.join(tmp, "config.json")))
+        raw["eos_token_id"] = free[4]                 # request 1 stops at its fifth token
+        json.dump(raw, open(os.path.join(tmp, "config.json"), "w"))
+        params = [SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True),
+                  SamplingParams(temperature=0.0, max_tokens=10),
+                  SamplingParams(temperature=0.8, top_k=40, top_p=0.95, max_tokens=7, ignore_eos=True, seed=5),
+                  SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True),
+                  SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)]
+        results = {}
+        for ahead in (False, True):
+            llm = LLM(tmp, dtype="float32", block_size=block, num_blocks=40, max_num_seqs=8, decode_run_ahead=ahead)
+            out = llm.generate(prompts, params)
+            results[ahead] = [(r.token_ids, r.finish_reason) for r in out]
+            engine = llm.engine
+            assert (engine.stats["run_ahead_steps"] > 0) == ahead
+            engine.runner.manager.check()
+            assert not engine.runner.manager.live_requests()
+            if ahead:
+                # abort while a step is in flight: the aborted row is dropped, the other request is not disturbed
+                engine.add_request("x", prompts[0], SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True))
+                engine.add_request("y", prompts[4], SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True))
+                got = {"x": [], "y": []}
+                steps = 0
+                while engine.has_requests():
+                    for o in engine.step():
+                        got[o.request_id].extend(o.new_token_ids)
+                    steps += 1
+                    if steps == 4:
+                        engine.abort(["x"])
+                assert got["y"] == results[True][4][0][:9] and len(got["x"]) < 9
+                engine.runner.manager.check()
+                assert not engine.runner.manager.live_requests()
+        assert results[True] == results[False]
+        assert results[True][1] == (free[:5], "stop")
+        assert results[True][0][0] == plain_qwen3.greedy_generate(pcfg, weights, prompts[0], 12)
+
+
 def test_decode_graphs_per_context_class(model_folders):
     """Decoding across a context-class boundary (512) switches to another captured graph; the tokens are those of
     the plain implementation, in 32-bit and (near-best) on the head-128 model in bfloat16."""
