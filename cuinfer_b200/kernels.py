@@ -295,7 +295,7 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots:
     return best
 
 
-DECODE_TMA_MIN_KEYS = 1536      # keys per CTA from which the TMA path of the decode kernel pays (measured)
+DECODE_TMA_MIN_KEYS = 1024      # keys per CTA from which the TMA path of the decode kernel pays (measured)
 
 
 def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
