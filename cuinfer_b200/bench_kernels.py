@@ -87,6 +87,25 @@ def attention_prefill(args) -> dict:
             "TFLOPs": round(flops / ms / 1e9, 1)}
 
 
+def norm(args) -> dict:
+    """Residual add + RMSNorm of ``--tokens`` rows of ``--hidden`` values (float32 residual, bfloat16 delta and output)."""
+    n, H = args.tokens, args.hidden
+    dev = "cuda:0"
+    copies = max(1, args.copies)
+    res = torch.randn(copies, n, H, device=dev)
+    delta = torch.randn(copies, n, H, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(copies, n, H, device=dev, dtype=torch.bfloat16)
+    w = torch.ones(H, device=dev, dtype=torch.bfloat16)
+
+    def run(i):
+        c = i % copies
+        kernels.add_rmsnorm(res[c], delta[c], w, 1e-6, out[c])
+
+    ms = _time(run, args.iters)
+    moved = n * H * (4 + 2 + 4 + 2)
+    return {"kernel": "add_rmsnorm", "tokens": n, "hidden": H, "ms": round(ms, 4), "GBps": round(moved / ms / 1e6, 1)}
+
+
 def gemm(args) -> dict:
     from .parts.linear import matmul_nt
 
@@ -171,6 +190,11 @@ def main(argv=None) -> int:
     ro.add_argument("--page-size", type=int, default=16)
     ro.add_argument("--copies", type=int, default=8)
     ro.add_argument("--iters", type=int, default=16)
+    no = sub.add_parser("norm", help=norm.__doc__)
+    no.add_argument("--tokens", type=int, default=2048)
+    no.add_argument("--hidden", type=int, default=1024)
+    no.add_argument("--copies", type=int, default=8, help="buffers rotated through, so that the L2 does not keep them")
+    no.add_argument("--iters", type=int, default=50)
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=8)
     g.add_argument("--n", type=int, default=4096)
@@ -181,7 +205,7 @@ def main(argv=None) -> int:
     g.add_argument("--copies", type=int, default=8)
     g.add_argument("--iters", type=int, default=20)
     args = p.parse_args(argv)
-    result = {"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm, "rope": rope}[args.kernel](args)
+    result = {"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm, "rope": rope, "norm": norm}[args.kernel](args)
     print(json.dumps(result))
     return 0
 

@@ -99,6 +99,60 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     }
 }
 
+// Many rows (prompt portions): a warp per row, the whole row in registers (CH chunks of four values per lane), every
+// load issued before the first use, one shuffle reduction, no second read of the residual.  Same arithmetic and the
+// same order of operations per element as the kernel above; only the order of the sum of squares differs.
+template <typename TD, typename TO, int CH>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ delta, AnyVec weight, float eps,
+                        TO* __restrict__ out, int hidden, int rows) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const size_t row = (size_t)r * hidden;
+    float x[CH][4], d[CH][4];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * 32 + lane) * 4;
+        if (i < hidden) Vec<float, 4>::load(residual + row + i, x[c]);
+    }
+    if (delta) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const int i = (c * 32 + lane) * 4;
+            if (i < hidden) Vec<TD, 4>::load(delta + row + i, d[c]);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * 32 + lane) * 4;
+        if (i < hidden) {
+            if (delta) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) x[c][k] += d[c][k];
+                Vec<float, 4>::store(residual + row + i, x[c]);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ss += x[c][k] * x[c][k];
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!out) return;
+    const float factor = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * 32 + lane) * 4;
+        if (i < hidden) {
+            float y[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) y[k] = x[c][k] * factor * weight[i + k];
+            Vec<TO, 4>::store(out + row + i, y);
+        }
+    }
+}
+
 // ---- gather of wanted rows ------------------------------------------------------------------------
 // out[s, :] = residual[idx[s], :] (+ delta[idx[s], :]) in 32 bits.
 template <typename TD>
@@ -171,7 +225,14 @@ extern "C" int cib_embedding_gather(const int* ids, const void* table, int table
 template <typename TD, typename TO>
 static void launch_add_rmsnorm(float* residual, const void* delta, AnyVec w, float eps, void* out, int rows,
                                int hidden, cudaStream_t stream) {
-    if (hidden % 4 == 0) {
+    // from 256 rows on and up to 2048 values a row: a warp per row
+    if (hidden % 4 == 0 && rows >= 256 && hidden <= 2048) {
+        const int ch = (hidden + 127) / 128;
+        const dim3 grid((rows + 7) / 8);
+        if (ch <= 4) add_rmsnorm_rows_kernel<TD, TO, 4><<<grid, 256, 0, stream>>>(residual, (const TD*)delta, w, eps, (TO*)out, hidden, rows);
+        else if (ch <= 8) add_rmsnorm_rows_kernel<TD, TO, 8><<<grid, 256, 0, stream>>>(residual, (const TD*)delta, w, eps, (TO*)out, hidden, rows);
+        else add_rmsnorm_rows_kernel<TD, TO, 16><<<grid, 256, 0, stream>>>(residual, (const TD*)delta, w, eps, (TO*)out, hidden, rows);
+    } else if (hidden % 4 == 0) {
         add_rmsnorm_kernel<TD, TO, 4><<<rows, norm_threads(hidden, 4), 0, stream>>>(residual, (const TD*)delta, w, eps, (TO*)out, hidden);
     } else {
         add_rmsnorm_kernel<TD, TO, 1><<<rows, norm_threads(hidden, 1), 0, stream>>>(residual, (const TD*)delta, w, eps, (TO*)out, hidden);

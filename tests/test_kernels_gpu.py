@@ -75,6 +75,29 @@ def test_add_rmsnorm(dtype, H, wdtype):
     close(out, P.rms_norm(res, w.float(), eps), TOL[dtype])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,H", [(256, 72), (301, 1000), (259, 1024), (257, 2048), (300, 2052)])
+def test_add_rmsnorm_many_rows(dtype, rows, H):
+    """From 256 rows on a warp takes a whole row (up to 2048 values; wider rows stay with the block kernel): widths
+    that do not fill the lanes, a last block with idle warps, and the add-only and norm-only forms."""
+    k = _k()
+    res = rand(rows, H, seed=12, scale=3.0)
+    delta = rand(rows, H, seed=13, dtype=dtype)
+    w = (1 + rand(H, seed=14, scale=0.2)).to(dtype)
+    r_dev = res.clone().to(DEV)
+    out = torch.full((rows, H), float("nan"), dtype=dtype, device=DEV)
+    k.add_rmsnorm(r_dev, delta.to(DEV), w.to(DEV), 2e-6, out)
+    x = res + delta.float()
+    close(r_dev, x, 1e-7)
+    close(out, P.rms_norm(x, w.float(), 2e-6), TOL[dtype])
+    r2 = res.clone().to(DEV)
+    k.add_rmsnorm(r2, None, w.to(DEV), 2e-6, out)                  # norm only
+    assert torch.equal(r2.cpu(), res)
+    close(out, P.rms_norm(res, w.float(), 2e-6), TOL[dtype])
+    k.add_rmsnorm(r2, delta.to(DEV), None, 2e-6, None)              # add only
+    close(r2, x, 1e-7)
+
+
 def test_gather_rows():
     k = _k()
     res, delta = rand(9, 83, seed=5), rand(9, 83, seed=6, dtype=torch.bfloat16)
