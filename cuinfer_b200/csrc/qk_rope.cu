@@ -184,7 +184,7 @@ constexpr int kBulkWarps = 8;
 constexpr int kBulkPasses = 4;
 
 template <typename T, int L>
-__global__ void __launch_bounds__(kBulkWarps * 32)
+__global__ void __launch_bounds__(kBulkWarps * 32, 4)
 qk_norm_rope_kv_write_bulk_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
                                   const int* __restrict__ slot_mapping, AnyVec q_weight, AnyVec k_weight, int has_norm,
                                   float eps, const float* __restrict__ rope_table, int has_rope, int max_positions,
@@ -192,8 +192,12 @@ qk_norm_rope_kv_write_bulk_kernel(T* __restrict__ qkv, int row_stride, const int
                                   int num_tokens) {
     constexpr int D = 8 * L, HPP = 32 / L;                    // heads per pass
     using Vec = Four<T>;
+    __shared__ __align__(16) float s_w[2][D];                 // the norms' gains (weights: not written by the kernel before)
+    if (has_norm)
+        for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) s_w[i / D][i % D] = i < D ? q_weight[i] : k_weight[i - D];
     griddep_launch();
     griddep_wait();
+    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_heads = write_cache ? nq + 2 * nkv : nq;
     const int groups = (total_heads + HPP * kBulkPasses - 1) / (HPP * kBulkPasses);
@@ -231,14 +235,6 @@ qk_norm_rope_kv_write_bulk_kernel(T* __restrict__ qkv, int row_stride, const int
         const float4 a = tp[0], b = tp[1];
         cs[0] = a.x, cs[1] = a.y, cs[2] = a.z, cs[3] = a.w, cs[4] = b.x, cs[5] = b.y, cs[6] = b.z, cs[7] = b.w;
     }
-    float wq[8], wk[8];
-    if (has_norm) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            wq[e] = q_weight[4 * li + e], wq[4 + e] = q_weight[D / 2 + 4 * li + e];
-            wk[e] = k_weight[4 * li + e], wk[4 + e] = k_weight[D / 2 + 4 * li + e];
-        }
-    }
 #pragma unroll
     for (int p = 0; p < kBulkPasses; ++p) {
         const int head = head_base + p * HPP + sub;
@@ -260,8 +256,11 @@ qk_norm_rope_kv_write_bulk_kernel(T* __restrict__ qkv, int row_stride, const int
 #pragma unroll
                 for (int o = L / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
                 const float factor = rsqrtf(ss / (float)D + eps);
+                const float4 wa = *reinterpret_cast<const float4*>(&s_w[kind][4 * li]);
+                const float4 wb = *reinterpret_cast<const float4*>(&s_w[kind][D / 2 + 4 * li]);
+                const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-                for (int e = 0; e < 8; ++e) x[e] = x[e] * factor * (kind == 0 ? wq[e] : wk[e]);
+                for (int e = 0; e < 8; ++e) x[e] = x[e] * factor * w[e];
             }
             if (has_rope) {
 #pragma unroll
