@@ -18,6 +18,7 @@
 // and of its values (128-byte swizzle), counted in bytes on an mbarrier per ring stage.  An SM keeps more bytes in
 // flight this way than its load/store unit allows for cp.async, which is what bounds a kernel that only streams.
 #include "mma_utils.cuh"
+#include "tcgen05_utils.cuh"
 
 #include <cuda.h>
 #include <string.h>
@@ -42,33 +43,6 @@ template <int D, bool TMA>
 __device__ __forceinline__ int block_off(int row, int chunk) {
     if (TMA) return (chunk >> 3) * (kDecKeys * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) * 8);
     return row * D + ((chunk ^ (row & 7)) * 8);
-}
-
-constexpr long long kDecWaitCycles = 400000000ll;     // about 0.2 s: a copy that has not landed by then never will
-
-__device__ __forceinline__ void dec_bar_init(uint64_t* b, uint32_t n) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(n));
-}
-__device__ __forceinline__ void dec_bar_expect(uint64_t* b, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool dec_bar_try(uint64_t* b, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool dec_bar_wait(uint64_t* b, uint32_t parity) {
-    if (dec_bar_try(b, parity)) return true;
-    const long long t0 = clock64();
-    while (clock64() - t0 < kDecWaitCycles)
-        if (dec_bar_try(b, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void dec_tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
 
 template <int D>
@@ -260,7 +234,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     if (TMA) {
         if (threadIdx.x == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
-            for (int i = 0; i < kDecWarps * kDecStages; ++i) dec_bar_init(&s_full[i], 1);
+            for (int i = 0; i < kDecWarps * kDecStages; ++i) mbar_init(&s_full[i], 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
@@ -278,11 +252,11 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         const long long row_k = okp ? (((long long)page * 2) * nkv + kvh) * page_size + off : total_rows;
         const long long row_v = okp ? row_k + (long long)nkv * page_size : total_rows;
         uint64_t* bar = &s_full[warp * kDecStages + s];
-        dec_bar_expect(bar, 2 * DecodeSmem<D>::kBlockBytes);
+        mbar_expect_tx(bar, 2 * DecodeSmem<D>::kBlockBytes);
 #pragma unroll
         for (int pn = 0; pn < D / 64; ++pn) {
-            dec_tma_load_2d(stage_k(s) + pn * kDecKeys * 64, &kv_map, bar, pn * 64, (int)row_k);
-            dec_tma_load_2d(stage_v(s) + pn * kDecKeys * 64, &kv_map, bar, pn * 64, (int)row_v);
+            tma_load_2d(stage_k(s) + pn * kDecKeys * 64, &kv_map, bar, pn * 64, (int)row_k);
+            tma_load_2d(stage_v(s) + pn * kDecKeys * 64, &kv_map, bar, pn * 64, (int)row_v);
         }
     };
 
@@ -378,7 +352,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     bool landed = true;
     for (int i = 0; i < my_blocks; ++i) {
         if (TMA) {
-            landed = dec_bar_wait(&s_full[warp * kDecStages + i % kDecStages], (uint32_t)((i / kDecStages) & 1));
+            landed = mbar_wait(&s_full[warp * kDecStages + i % kDecStages], (uint32_t)((i / kDecStages) & 1));
             landed = __all_sync(0xffffffffu, landed);
             if (!landed) {
                 if (lane == 0) atomicExch(error_flag, 21);

@@ -23,8 +23,7 @@
 // Every mbarrier wait is bounded; on a time-out the kernel raises the error flag, stops, frees its tensor memory
 // and returns.
 #include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05_utils.cuh"
 
 namespace cib {
 namespace fa {
@@ -33,60 +32,15 @@ constexpr int kD = 128;          // head size
 constexpr int kM = 128;          // rows per CTA
 constexpr int kN = 128;          // keys per tile
 constexpr int kPanel = kM * 128; // bytes of one 64-column panel of a 128-row tile
-constexpr long long kWaitCycles = 400000000ll;     // about 0.2 s
 
-__device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void bar_init(uint64_t* b, uint32_t n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n)); }
-__device__ __forceinline__ void bar_expect(uint64_t* b, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bar_arrive(uint64_t* b) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory"); }
-__device__ __forceinline__ bool bar_try(uint64_t* b, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool bar_wait(uint64_t* b, uint32_t parity) {
-    if (bar_try(b, parity)) return true;
-    const long long t0 = clock64();
-    while (clock64() - t0 < kWaitCycles)
-        if (bar_try(b, parity)) return true;
-    return false;
-}
-// K-major operand, 128-byte swizzle: 8-row atoms 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_kmajor(const void* smem) {
-    return (uint64_t)((s32(smem) & 0x3ffff) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
 // MN-major operand (values: [key][d], d contiguous), 128-byte swizzle: 64-element panels `panel_bytes` apart (leading
 // offset), 8-key groups 1024 bytes apart (stride offset).
 __device__ __forceinline__ uint64_t desc_mnmajor(const void* smem, uint32_t panel_bytes) {
-    return (uint64_t)((s32(smem) & 0x3ffff) >> 4) | ((uint64_t)(panel_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+    return (uint64_t)((tc_smem_u32(smem) & 0x3ffff) >> 4) | ((uint64_t)(panel_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 // D = F32, A = B = BF16, M = 128, N = 128; b_mn: B is MN-major.
 __host__ __device__ constexpr uint32_t idesc(bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-}
-__device__ __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t id, uint32_t acc) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d), "l"(a), "l"(b), "r"(id), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void commit(uint64_t* b) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(b)) : "memory");
-}
-__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
 }
 __device__ __forceinline__ void tst32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -99,7 +53,6 @@ __device__ __forceinline__ void tst32(uint32_t taddr, const uint32_t (&r)[32]) {
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
-__device__ __forceinline__ void tld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tst_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // shared memory: Q | K0 | K1 | V0 | V1, each 128 rows x 128 columns bf16 = 32 KB as two 64-column panels.  (A third key
@@ -115,12 +68,6 @@ constexpr int kThreads = (kMmaWarp + 3) * 32;      // + the MMA warp, a producer
 __device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t id, uint32_t acc) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                  ::"r"(d), "r"(a_tmem), "l"(b), "r"(id), "r"(acc) : "memory");
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(s32(smem_dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1) : "memory");
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -161,24 +108,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             t -= tiles;
         }
         s_req = r; s_tile = t; s_abort = 0;
-        for (int i = 0; i < kKBufs; ++i) { bar_init(&k_full[i], 1); bar_init(&k_free[i], 1); }
+        for (int i = 0; i < kKBufs; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_free[i], 1); }
         for (int i = 0; i < 2; ++i) {
-            bar_init(&v_full[i], 1); bar_init(&v_free[i], 1); bar_init(&s_full[i], 1);
-            bar_init(&p_ready[i], 8); bar_init(&pv_done[i], 1);
+            mbar_init(&v_full[i], 1); mbar_init(&v_free[i], 1); mbar_init(&s_full[i], 1);
+            mbar_init(&p_ready[i], 8); mbar_init(&pv_done[i], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == kMmaWarp) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // stale shared memory must at least be finite: rows of a tile that no page covers are multiplied by P = 0
     for (int i = tid; i < (kKBufs + kVBufs) * kTileBytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(sK)[i] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // before the bulk copies write the same bytes
-    fence_before();
+    tcgen05_fence_before();
     __syncthreads();
-    fence_after();
+    tcgen05_fence_after();
     const uint32_t tmem = *tmem_slot;
     const int r = s_req;
     const bool active = r < num_requests;
@@ -219,23 +166,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
         auto issue_s = [&](int j) {
             if (lane != 0) return;
             const int b = j & 1;
-            const uint64_t qd = desc_kmajor(sQ), kd = desc_kmajor(sK + (j % kKBufs) * kTileBytes);
+            const uint64_t qd = umma_desc_k_major_sw128(sQ), kd = umma_desc_k_major_sw128(sK + (j % kKBufs) * kTileBytes);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const uint64_t off = (uint64_t)(((k >> 2) * kPanel + (k & 3) * 32) >> 4);
-                mma(tmem + (uint32_t)(b * kN), qd + off, kd + off, idesc(false), k != 0);
+                umma_bf16(tmem + (uint32_t)(b * kN), qd + off, kd + off, idesc(false), k != 0);
             }
-            commit(&s_full[b]);
-            commit(&k_free[j % kKBufs]);    // the key buffer can be refilled as soon as S has been computed
+            umma_commit(&s_full[b]);
+            umma_commit(&k_free[j % kKBufs]);    // the key buffer can be refilled as soon as S has been computed
         };
         auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
-            bool ok = bar_wait(bar, parity);
+            bool ok = mbar_wait(bar, parity);
             if (!ok && lane == 0) { atomicExch(error_flag, code); s_abort = 1; }
             return __all_sync(0xffffffffu, ok);
         };
         bool ok = true;
         ok = wait_all(&k_full[0], 0, 11);
-        if (ok) { fence_after(); issue_s(0); }
+        if (ok) { tcgen05_fence_after(); issue_s(0); }
         for (int j = 0; j < num_tiles && ok; ++j) {
             const int b = j & 1;
             const uint32_t parity = (j >> 1) & 1;
@@ -244,7 +191,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                 // runs what one thread issues in order
                 ok = wait_all(&k_full[(j + 1) % kKBufs], ((j + 1) / kKBufs) & 1, 12);
                 if (!ok) break;
-                fence_after();
+                tcgen05_fence_after();
                 issue_s(j + 1);
             }
             ok = wait_all(&p_ready[b], parity, 13) && wait_all(&v_full[b], parity, 14);
@@ -265,7 +212,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                     __syncwarp();
                 }
             }
-            fence_after();
+            tcgen05_fence_after();
             if (lane == 0) {
                 // O_b += P V: P is the A operand straight from tensor memory (16 keys = 8 columns per step)
 #pragma unroll
@@ -273,8 +220,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                     const uint64_t vd = desc_mnmajor(sV + b * kTileBytes + k * 16 * 128, kPanel);
                     mma_ts(tmem + (uint32_t)(2 * kN + b * kN), tmem + (uint32_t)(b * kN + k * 8), vd, idesc(true), (j >= 2) || k != 0);
                 }
-                commit(&pv_done[b]);
-                commit(&v_free[b]);         // the value buffer can be refilled
+                umma_commit(&pv_done[b]);
+                umma_commit(&v_free[b]);         // the value buffer can be refilled
             }
             __syncwarp();
         }
@@ -303,7 +250,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             const int key0 = k_lo + t * kN;
             uint64_t* bar = kv ? &v_full[b] : &k_full[b];
             const int nvalid = min(boxes, max(0, (seq_len - key0 + box_rows - 1) / box_rows));
-            if (lane == 0) bar_expect(bar, (uint32_t)(nvalid * 2 * box_rows * 128));
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)(nvalid * 2 * box_rows * 128));
             __syncwarp();
             if (box < nvalid) {
                 const int off = (key0 + box * box_rows) % page_size;        // not 0 only for pages longer than a tile
@@ -313,7 +260,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             }
         };
         auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
-            bool ok = bar_wait(bar, parity);
+            bool ok = mbar_wait(bar, parity);
             if (!ok && lane == 0) { atomicExch(error_flag, code); s_abort = 1; }
             return __all_sync(0xffffffffu, ok);
         };
@@ -350,20 +297,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
         for (int j = grp; j < num_tiles; j += 2, ++done) {
             const uint32_t parity = (uint32_t)(done & 1);
             const int key0 = k_lo + j * kN;
-            ok = bar_wait(&s_full[grp], parity);
+            ok = mbar_wait(&s_full[grp], parity);
             if (!ok && lane == 0) { atomicExch(error_flag, 15); s_abort = 1; }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
             if (!ok) break;
-            fence_after();
+            tcgen05_fence_after();
             const bool need_mask = key0 + kN - 1 > pos || window > 0;
             const int hi = pos - key0;                              // columns <= hi are visible ...
             const int lo = window > 0 ? hi - window : -1;           // ... and > lo
             // this thread's 64 scores, read from tensor memory once; masked ones become -inf here, so that the
             // maximum (the scale is positive: applied afterwards) and the exponentials need no second look at the mask
             uint32_t v[64];
-            tld32(lane_addr + s_col + (uint32_t)cb, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-            tld32(lane_addr + s_col + (uint32_t)(cb + 32), *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-            tld_wait();
+            tmem_ld_32x32b_x32(lane_addr + s_col + (uint32_t)cb, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            tmem_ld_32x32b_x32(lane_addr + s_col + (uint32_t)(cb + 32), *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            tmem_ld_wait();
             float mx = -INFINITY;
             if (need_mask) {
 #pragma unroll
@@ -404,16 +351,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             }
             // the group's O is only touched once P V of its tile before has finished
             if (done > 0 && __any_sync(0xffffffffu, rescale)) {
-                ok = bar_wait(&pv_done[grp], (uint32_t)((done - 1) & 1));
+                ok = mbar_wait(&pv_done[grp], (uint32_t)((done - 1) & 1));
                 if (!ok && lane == 0) { atomicExch(error_flag, 16); s_abort = 1; }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
-                fence_after();
+                tcgen05_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < 2; ++c) {
                     uint32_t o[32];
-                    tld32(lane_addr + o_col + (uint32_t)(cb + c * 32), o);
-                    tld_wait();
+                    tmem_ld_32x32b_x32(lane_addr + o_col + (uint32_t)(cb + c * 32), o);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * (rescale ? corr : 1.f));
                     tst32(lane_addr + o_col + (uint32_t)(cb + c * 32), o);
@@ -423,21 +370,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             // both threads hold in registers since the barrier above
             tst32(lane_addr + s_col + (uint32_t)(half * 32), p);
             tst_wait();
-            fence_before();
+            tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) bar_arrive(&p_ready[grp]);
+            if (lane == 0) mbar_arrive(&p_ready[grp]);
         }
         // ---- merge the two groups: O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)) ----
         if (ok && done > 0) {
-            ok = bar_wait(&pv_done[grp], (uint32_t)((done - 1) & 1));
+            ok = mbar_wait(&pv_done[grp], (uint32_t)((done - 1) & 1));
             if (!ok && lane == 0) { atomicExch(error_flag, 17); s_abort = 1; }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
         s_l[grp][half][row_local] = l;
         if (half == 0) s_m[grp][row_local] = m_used;
-        fence_before();
+        tcgen05_fence_before();
         asm volatile("bar.sync 9, %0;" ::"r"(kMmaWarp * 32) : "memory");      // the sixteen softmax warps
-        fence_after();
+        tcgen05_fence_after();
         if (!(*(volatile int*)&s_abort) && num_tiles > 0) {
             // group grp stores the output columns 32 grp .. + 31 of this thread's half of the head
             const float m0 = s_m[0][row_local], m1 = s_m[1][row_local];
@@ -449,9 +396,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             const float f0 = w0 * inv, f1 = w1 * inv;
             const bool has1 = num_tiles > 1;        // group 1 has an accumulator only if there was a second tile
             uint32_t a[32], b[32];
-            tld32(lane_addr + (uint32_t)(2 * kN + cb + grp * 32), a);
-            if (has1) tld32(lane_addr + (uint32_t)(3 * kN + cb + grp * 32), b);
-            tld_wait();
+            tmem_ld_32x32b_x32(lane_addr + (uint32_t)(2 * kN + cb + grp * 32), a);
+            if (has1) tmem_ld_32x32b_x32(lane_addr + (uint32_t)(3 * kN + cb + grp * 32), b);
+            tmem_ld_wait();
             if (row_ok) {
                 const int tl = grow / g, hh = grow % g;
                 __nv_bfloat16* dst = out + (size_t)(q0 + tl) * out_stride + (size_t)(kvh * g + hh) * kD + cb + grp * 32;
@@ -473,7 +420,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             }
         }
     }
-    fence_before();
+    tcgen05_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
 }
