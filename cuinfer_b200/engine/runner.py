@@ -372,7 +372,10 @@ class ModelRunner:
             self._timing_start = None
 
     # ---- decode steps as CUDA graphs ---------------------------------------------------------------------
-    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+    # Row counts a graph is captured for.  Between powers of two there is a step in between: the launch shapes of a
+    # graph (above all how the attention kernel splits the keys) are chosen for the bucket's rows, and 17 requests in a
+    # graph made for 32 ran their attention at two thirds of the bandwidth of 16 in a graph made for 16.
+    GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
     # A graph is also captured per class of context length: how the decode attention kernel splits the keys over
     # CTAs is fixed at capture, and a split chosen for the model's longest context is a poor one for short ones.
     GRAPH_CONTEXTS = (512, 2048, 8192, 32768, 131072)
