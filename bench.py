@@ -233,6 +233,7 @@ def reference_arm() -> int:
 
 
 def main() -> int:
+    global MODEL, MODEL_NAME, CONTEXT
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=256)
@@ -242,13 +243,17 @@ def main() -> int:
     parser.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes (default: the 0.6B shape)")
     parser.add_argument("--layers", type=int, default=0,
                         help="fewer layers than the configuration's, if memory or time needs it (reported)")
+    parser.add_argument("--context", type=int, default=CONTEXT,
+                        help="tokens a request holds when decoding ends (default: the baseline's context length)")
     parser.add_argument("--disable-cuda-graph", action="store_true")
     parser.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the prefill measurement")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
-    global MODEL, MODEL_NAME
     MODEL_NAME, MODEL = SHAPES[args.shape]
+    if args.context != CONTEXT:
+        CONTEXT = args.context
+        MODEL = dict(MODEL, max_position_embeddings=max(CONTEXT, MODEL["max_position_embeddings"]))
     if args.layers <= 0:
         args.layers = MODEL["num_hidden_layers"]
     if args.gpus != 1:
