@@ -256,3 +256,70 @@ def test_command_line(model_folders, tmp_path):
     bad = subprocess.run([sys.executable, "-m", "cuinfer_b200", "generate", "--model", folder, "--prompt-ids", "1",
                           "--block-size", "0"], capture_output=True, text=True, cwd=ROOT, timeout=300)
     assert bad.returncode != 0 and "block_size" in bad.stderr
+
+
+def test_random_workloads_do_not_depend_on_engine_settings(model_folders):
+    """Requests that arrive over time with random lengths, budgets and sampling options (greedy and seeded), some
+    aborted on the way: float32 outputs are the same with and without CUDA graphs and run-ahead, with pages so few that
+    requests are preempted and recomputed, and with a small token budget and few sequences."""
+    import random
+
+    from cuinfer_b200 import SamplingParams
+    from cuinfer_b200.config import EngineConfig
+    from cuinfer_b200.engine.core import EngineCore
+
+    folders, cfg, block = model_folders["B"]
+    folder, vocab, longest = folders["float32"], cfg["vocab_size"], cfg["max_position_embeddings"]
+
+    def workload(seed):
+        rnd = random.Random(seed)
+        requests = []
+        for i in range(rnd.randint(12, 24)):
+            budget = rnd.choice([1, 2, 3, 8, 20, 40])
+            n = min(rnd.choice([1, 2, 5, 17, 33, 64, 100, 150]), longest - budget - 1)
+            greedy = rnd.random() < 0.6
+            params = SamplingParams(temperature=0.0 if greedy else rnd.choice([0.7, 1.0]), top_k=0 if greedy else rnd.choice([0, 20]),
+                                    top_p=1.0 if greedy else rnd.choice([1.0, 0.9]), max_tokens=budget,
+                                    ignore_eos=rnd.random() < 0.7, seed=None if greedy else rnd.randint(0, 99))
+            requests.append(dict(id=f"r{i}", arrive=rnd.randint(0, 12), prompt=random_tokens(vocab, n, seed * 100 + i),
+                                 params=params, abort_at=rnd.randint(3, 30) if rnd.random() < 0.15 else None))
+        return requests
+
+    def run(requests, **options):
+        engine = EngineCore(EngineConfig(model_path=folder, dtype="float32", block_size=block, seed=1, **options))
+        tokens, reasons = {r["id"]: [] for r in requests}, {}
+        pending = sorted(requests, key=lambda r: r["arrive"])
+        step = 0
+        while pending or engine.has_requests():
+            while pending and pending[0]["arrive"] <= step:
+                r = pending.pop(0)
+                engine.add_request(r["id"], r["prompt"], r["params"])
+            engine.abort([r["id"] for r in requests if r["abort_at"] == step and r["id"] in engine.scheduler.requests])
+            for out in engine.step():
+                tokens[out.request_id].extend(out.new_token_ids)
+                reasons[out.request_id] = out.finish_reason.value
+            step += 1
+            assert step < 3000, "no progress"
+        engine.runner.manager.check()
+        assert not engine.runner.manager.live_requests()
+        return tokens, reasons, engine
+
+    roomy = dict(num_blocks=400, max_num_seqs=16, max_num_scheduled_tokens=256)
+    preempted = ahead = 0
+    for seed in (10, 11, 12):
+        requests = workload(seed)
+        want, want_reasons, _ = run(requests, enable_cuda_graph=False, decode_run_ahead=False, **roomy)
+        for options in (roomy, dict(roomy, decode_run_ahead=False),
+                        dict(roomy, num_blocks=(190 + block - 1) // block + 3),
+                        dict(roomy, max_num_seqs=4, max_num_scheduled_tokens=48)):
+            got, reasons, engine = run(requests, **options)
+            preempted += engine.scheduler.num_preemptions
+            ahead += engine.stats["run_ahead_steps"]
+            for r in requests:
+                rid = r["id"]
+                if r["abort_at"] is not None or "capacity" in (reasons.get(rid), want_reasons.get(rid)):
+                    common = min(len(got[rid]), len(want[rid]))     # how far it got depends on the schedule
+                    assert got[rid][:common] == want[rid][:common], (seed, options, rid)
+                else:
+                    assert got[rid] == want[rid] and reasons.get(rid) == want_reasons.get(rid), (seed, options, rid)
+    assert preempted > 0 and ahead > 0
