@@ -164,12 +164,14 @@ def measure_decode(folder: str, batch: int, steps: int, warmup: int, args, sampl
     launches_before = kernels.launch_count
     graph_before = engine.runner.graph_steps
     torch.cuda.synchronize()
+    torch.cuda.nvtx.range_push(f"timed_decode_b{batch}")      # lets a profiler pick the timed launches (--nvtx-include)
     t0 = time.perf_counter()
     tokens = 0
     for _ in range(steps):
         tokens += sum(len(o.new_token_ids) for o in engine.step())
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
+    torch.cuda.nvtx.range_pop()
     clock_info = clocks.stop() if sample_clocks else None
     device_ms = sum(a.elapsed_time(b) for a, b in engine.runner.timing)
     pairs = len(engine.runner.timing)
@@ -210,7 +212,11 @@ def measure_prefill(folder: str, args) -> dict:
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         a.record()
+        if it >= 3:
+            torch.cuda.nvtx.range_push("timed_prefill")
         logits = runner.step([StepEntry("p", tokens, [PREFILL_TOKENS - 1])])
+        if it >= 3:
+            torch.cuda.nvtx.range_pop()
         b.record()
         torch.cuda.synchronize()
         runner.release("p")
