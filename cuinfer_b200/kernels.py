@@ -80,6 +80,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_gemm_wstream": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
         "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
+        "cib_argmax_rows": [_P, _I, _I, _I, _P, _P],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -629,6 +630,17 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, silu_pair:
 
 
 # ---- sampling ----------------------------------------------------------------------------------------
+
+def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
+    """out_ids[s] = index of the largest of logits[s] (float32), ties to the lowest index: greedy sampling of every row."""
+    S, V = logits.shape
+    if logits.stride(1) != 1 or out_ids.numel() < S:
+        raise KernelError("argmax_rows: logits rows must be dense and out_ids hold a row each")
+    rc = library().cib_argmax_rows(_cuda(logits, "logits", torch.float32, contiguous=False), logits.stride(0), S, V,
+                                   _cuda(out_ids, "out_ids", torch.int32), _stream())
+    _check(rc, "argmax_rows")
+    _count()
+
 
 def sample(logits: torch.Tensor, params: torch.Tensor, out_ids: torch.Tensor) -> None:
     """out_ids[s] = token drawn from logits[s]; params[s] = (temperature, top_k as int bits, top_p, u)."""

@@ -32,9 +32,6 @@ def uniform(seed: int, request_key: int, output_index: int) -> float:
     return (h >> 40) / float(1 << 24)
 
 
-_GREEDY = SamplingParams(temperature=0.0)
-
-
 class Sampler:
     def __init__(self, seed: int, device: torch.device, max_rows: int) -> None:
         self.seed = seed
@@ -47,7 +44,6 @@ class Sampler:
         self._host = self._hosts[0]
         self._dev = torch.empty((max(1, max_rows), 4), dtype=torch.float32, device=device)
         self._ids = torch.empty(max(1, max_rows), dtype=torch.int32, device=device)
-        self._greedy_rows = 0          # leading rows of the device buffer that hold plain argmax options
 
     def _next_host(self) -> None:
         self._turn = (self._turn + 1) % len(self._hosts)
@@ -78,18 +74,13 @@ class Sampler:
         rows = len(params)
         if logits.shape[0] != rows:
             raise ValueError(f"{logits.shape[0]} logits rows for {rows} requests")
-        if all(p.greedy for p in params):
-            # argmax rows need no uniform number: the packed rows on the device stay valid from step to step
-            if self._greedy_rows < rows:
-                self._next_host()
-                self.pack([_GREEDY] * rows, [0] * rows, [0] * rows)
-                self._upload(rows)
-                self._greedy_rows = rows
-        else:
-            self._next_host()
-            self.pack(params, request_keys, output_indices)
-            self._upload(rows)
-            self._greedy_rows = 0
         out = self._ids[:rows]
+        if all(p.greedy for p in params):
+            # every row is an argmax: no options, no uniform numbers, and eight CTAs to a row
+            kernels.argmax_rows(logits, out)
+            return out
+        self._next_host()
+        self.pack(params, request_keys, output_indices)
+        self._upload(rows)
         kernels.sample(logits, self._dev[:rows], out)
         return out

@@ -591,3 +591,27 @@ def test_sampler_against_plain(V):
     assert sum(a != b for a, b in zip(got, want)) == 0
     kth = torch.sort(logits[4], descending=True).values[29]
     assert all(logits[4, t] >= kth for t in got)
+
+
+@pytest.mark.parametrize("V, ld", [(517, 517), (1000, 1003), (151936, 151936), (5, 8), (64, 64)])
+def test_argmax_rows(V, ld):
+    """Greedy sampling of every row by clusters of eight CTAs: the largest value, ties to the lowest id, the same
+    answers as the general sampling kernel; rows that are not 16-byte aligned, vocabularies smaller than the threads."""
+    k = _k()
+    g = torch.Generator().manual_seed(41)
+    rows = 9
+    wide = torch.randn(rows, ld, generator=g) * 3
+    logits = wide[:, :V]
+    top = float(logits.max()) + 1
+    logits[1, V - 1] = logits[1, V // 2] = top                 # a tie across the CTAs' shares: the lower id wins
+    logits[2, 0] = top
+    logits[3, V - 1] = top
+    logits[4] = -float("inf")                                  # nothing to choose: id 0
+    logits[5, : max(1, V // 3)] = float("nan")                 # values that are not numbers never win
+    dev = wide.to(DEV)[:, :V]
+    out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    k.argmax_rows(dev, out)
+    got = out.cpu().tolist()
+    want = [P.sample_plain(torch.nan_to_num(logits[i], nan=-float("inf")), 0.0, 0, 1.0, 0.5) for i in range(rows)]
+    assert got == want and got[1] == V // 2 and got[2] == 0 and got[3] == V - 1 and got[4] == 0
+    assert got == _sample(k, logits.contiguous(), [(0.0, 0, 1.0, 0.5)] * rows)
