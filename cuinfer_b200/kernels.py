@@ -298,6 +298,18 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots:
 
 DECODE_TMA_MIN_KEYS = 1024      # keys per CTA from which the TMA path of the decode kernel pays (measured)
 
+# A kernel of the decode chain may ask for the weights of the kernel after it to be fetched into the L2 while it runs.
+# That pays where the chain is bound by latencies and the weights are small beside the 126 MB L2 (every matrix of the
+# 0.6B layer sizes is under 13 MB).  Matrices of 33 to 200 MB (the 8B layer sizes) would compete with the running
+# kernel's own stream and could not stay in the L2 until they are used, so larger ones are not asked for.
+L2_HINT_MAX_BYTES = 16 << 20
+
+
+def _l2_hint(warm: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if warm is None or warm.numel() * warm.element_size() > L2_HINT_MAX_BYTES:
+        return None
+    return warm
+
 
 def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                            seq_lens: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
@@ -308,6 +320,7 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
     streams faster but starts slower, so callers that know the keys per CTA pass False for short streams.
     ``warm``: a tensor that the kernel after this one reads first; fetched into the L2 when the stream of keys ends."""
     R = q.shape[0]
+    warm = _l2_hint(warm)
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("paged_attention_decode: bfloat16 only")
     if q.stride(1) != 1 or out.stride(1) != 1 or out.shape != (R, num_q_heads * head_dim):
@@ -463,6 +476,7 @@ def gemm_skinny(w: torch.Tensor, out: torch.Tensor, *, act: torch.Tensor | None 
     ``out`` float32 selects the 32-bit store."""
     N, K = w.shape
     M = out.shape[0]
+    warm = _l2_hint(warm)
     if w.dtype != torch.bfloat16 or w.stride(1) != 1:
         raise KernelError("gemm_skinny: weights must be bfloat16 with dense rows")
     if silu_pair:
