@@ -228,13 +228,130 @@ def measure_prefill(folder: str, args) -> dict:
     return {"ms": statistics.median(times)}
 
 
-def reference_arm() -> int:
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "pip installs only the reference's Python front end into baseline/_ref; its engine (cuinfer._C) "
-                       "is a CMake build that fetches libzmq, cppzmq, msgpack-cxx and nlohmann_json from GitHub (no "
-                       "network here), it serves HTTP only, has no random-weights mode, and its kernels accept only "
-                       "hidden 1024/2048 with a downloaded checkpoint"}))
+def write_reference_model(folder: str, cfg: dict, seed: int) -> None:
+    """A model folder for the reference arm, written without any of this repository's code: the tensor names and
+    shapes the reference looks up (csrc/model/causal_lm.cpp:35-53, csrc/model/layers/attention.cpp:22-40,
+    csrc/model/layers/mlp.cpp:12-17) as bfloat16 N(0, 0.02), gains 1, in one safetensors file."""
+    import struct
+
+    import torch
+
+    H, I, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    Q, KV = cfg["num_attention_heads"] * d, cfg["num_key_value_heads"] * d
+    shapes = {"model.embed_tokens.weight": (cfg["vocab_size"], H), "model.norm.weight": (H,)}
+    if not cfg["tie_word_embeddings"]:
+        shapes["lm_head.weight"] = (cfg["vocab_size"], H)
+    for i in range(cfg["num_hidden_layers"]):
+        pre = f"model.layers.{i}."
+        shapes.update({
+            pre + "input_layernorm.weight": (H,), pre + "post_attention_layernorm.weight": (H,),
+            pre + "self_attn.q_proj.weight": (Q, H), pre + "self_attn.k_proj.weight": (KV, H),
+            pre + "self_attn.v_proj.weight": (KV, H), pre + "self_attn.o_proj.weight": (H, Q),
+            pre + "self_attn.q_norm.weight": (d,), pre + "self_attn.k_norm.weight": (d,),
+            pre + "mlp.gate_proj.weight": (I, H), pre + "mlp.up_proj.weight": (I, H), pre + "mlp.down_proj.weight": (H, I)})
+    header, offset = {}, 0
+    for name, shape in shapes.items():
+        size = 2
+        for n in shape:
+            size *= n
+        header[name] = {"dtype": "BF16", "shape": list(shape), "data_offsets": [offset, offset + size]}
+        offset += size
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    blob += b" " * (-len(blob) % 8)
+    gen = torch.Generator().manual_seed(seed)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as fh:
+        fh.write(struct.pack("<Q", len(blob)))
+        fh.write(blob)
+        for name, shape in shapes.items():
+            if name.endswith("norm.weight"):
+                t = torch.ones(shape, dtype=torch.bfloat16)
+            else:
+                t = (torch.randn(shape, generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            fh.write(t.view(torch.int16).numpy().tobytes())
+    with open(os.path.join(folder, "config.json"), "w") as fh:
+        json.dump(dict(cfg, eos_token_id=cfg["vocab_size"] - 1), fh)
+
+
+def reference_arm(args) -> int:
+    """The same metric on the same configuration through the UNMODIFIED reference engine: its scheduler and model
+    runner (stock kernels, cuBLAS, CUDA graphs, sampler) driven by ``baseline/reference_bench.cpp``, which runs the
+    loop of csrc/engine/engine_core.cpp:93-105 without the socket.  Nothing of cuinfer_b200 is imported."""
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())[:600]}))
+        return 0
+
+    if args.shape != "0.6b" or args.layers not in (0, MODEL["num_hidden_layers"]):
+        return unavailable("the reference's kernels take hidden size 1024 or 2048 only (csrc/ops/rms_norm.cu:115-130); "
+                           "the arm runs the 0.6B shape at full depth")
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import build_reference
+        binary = build_reference.build()
+    except Exception as exc:      # noqa: BLE001 - any build problem makes the arm unavailable, with its message
+        return unavailable(f"the reference engine could not be built here: {exc}")
+    if shutil.which("nvidia-smi") is None:
+        return unavailable("no GPU on this machine")
+    args.warmup = max(args.warmup, 3)
+    cfg = dict(MODEL, max_position_embeddings=CONTEXT)
+    tmp = tempfile.mkdtemp(prefix="cuinfer_reference_bench_")
+
+    def run(batch: int, steps: int, prefill_tokens: int) -> dict:
+        cmd = [binary, "--mode", "bench", "--model", tmp, "--batch", str(batch), "--context", str(CONTEXT),
+               "--steps", str(steps), "--warmup", str(args.warmup), "--prefill-tokens", str(prefill_tokens),
+               "--block-size", str(BLOCK_SIZE), "--max-num-scheduled-tokens", "8192", "--max-num-seqs", "256",
+               "--gpu-memory-utilization", "0.9", "--seed", "1234"]
+        if args.disable_cuda_graph:
+            cmd.append("--disable-cuda-graph")
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+        if proc.returncode != 0:
+            raise RuntimeError(f"reference_bench exited with {proc.returncode}: {proc.stderr[-400:]}")
+        return json.loads(proc.stdout.strip().splitlines()[-1])
+
+    try:
+        write_reference_model(tmp, cfg, seed=0)
+        clocks = ClockSampler()
+        clocks.start()
+        main_run = run(args.batch, args.steps, PREFILL_TOKENS if not args.skip_points else 0)
+        clock_info = clocks.stop()
+        points = {}
+        if not args.skip_points:
+            for b in (1, 64):
+                r = run(b, min(args.steps, 128), 0)
+                points[f"decode_b{b}"] = round(b * 1e3 / r["device_ms_per_step"], 1)
+    except Exception as exc:      # noqa: BLE001
+        return unavailable(f"the reference engine did not run: {exc}")
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+    peaks = load_peaks()
+    line = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2048 tokens; % of roofline",
+        "value": round(args.batch * 1e3 / main_run["device_ms_per_step"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(main_run["device_ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) seed 0, uniform-random token ids", "impl": "reference",
+        "config": {
+            "model": MODEL_NAME, "layers": MODEL["num_hidden_layers"], "layers_full": MODEL["num_hidden_layers"],
+            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "tied_embeddings": True, "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": main_run["prompt_len"],
+            "kv_block_size": BLOCK_SIZE, "parallelism": "single GPU", "cuda_graph": not args.disable_cuda_graph,
+            "l2": "no flush: each step reads >1 GB, far more than the 126 MB L2", "peaks": peaks["source"],
+        },
+        "e2e": {"value": round(args.batch * 1e3 / main_run["ms_per_step"], 1), "unit": "tokens/s",
+                "ms_per_step": round(main_run["ms_per_step"], 4),
+                "h2d_bytes_per_step": main_run["h2d_bytes_per_step"], "d2h_bytes_per_step": main_run["d2h_bytes_per_step"]},
+        "gpu_launches": None,
+        "clocks": clock_info,
+    }
+    if main_run.get("prefill_ms"):
+        line["prefill"] = {"value": round(PREFILL_TOKENS * 1e3 / main_run["prefill_ms"], 1), "tokens": PREFILL_TOKENS,
+                           "ms": round(main_run["prefill_ms"], 3),
+                           "frac": round(prefill_flops(cfg, cfg["num_hidden_layers"], PREFILL_TOKENS)
+                                         / (main_run["prefill_ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+    if points:
+        line["points"] = points
+    print(json.dumps(line))
     return 0
 
 
@@ -255,7 +372,7 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the prefill measurement")
     args = parser.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     MODEL_NAME, MODEL = SHAPES[args.shape]
     if args.context != CONTEXT:
         CONTEXT = args.context
