@@ -114,6 +114,7 @@ class SlotPool:
 @dataclass
 class _Held:
     slot: int
+    serial: int = 0                                             # number of this admission; never handed out twice
     num_tokens: int = 0                                         # tokens whose keys/values are stored
     tables: List[List[int]] = field(default_factory=list)       # per group: page of every page index, -1 if given back
     first_live: List[int] = field(default_factory=list)         # per group: first page index still held
@@ -132,6 +133,7 @@ class CacheManager:
         self.pools = [PagePool(n) for n in counts]
         self.slots = SlotPool(max_requests)
         self._held: Dict[Hashable, _Held] = {}
+        self._admissions = 0
         self.newly_admitted: List[int] = []   # slots whose state must be zeroed before the next step
 
     # ---- queries ---------------------------------------------------------------------------------
@@ -146,6 +148,12 @@ class CacheManager:
 
     def slot(self, request_id: Hashable) -> int:
         return self._get(request_id).slot
+
+    def serial(self, request_id: Hashable) -> int:
+        """The number of the admission under which the request holds its pages.  A request id that comes back
+        after its release (a caller's conversation id, a preempted request) gets a new one, so anything cached per
+        request outside the manager — block-table rows already on the device — can tell the two apart."""
+        return self._get(request_id).serial
 
     def block_table(self, request_id: Hashable, group: int = 0) -> List[int]:
         """Page of every page index of the request in ``group``; -1 where the page was given back."""
@@ -179,7 +187,9 @@ class CacheManager:
         if slot is None:
             return None
         n = len(self.groups)
-        self._held[request_id] = _Held(slot=slot, tables=[[] for _ in range(n)], first_live=[0] * n)
+        self._admissions += 1
+        self._held[request_id] = _Held(slot=slot, serial=self._admissions, tables=[[] for _ in range(n)],
+                                       first_live=[0] * n)
         self.newly_admitted.append(slot)
         return slot
 

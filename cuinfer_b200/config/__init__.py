@@ -1,5 +1,5 @@
 from .engine_config import EngineConfig
-from .model_config import ConfigError, Qwen3Config, read_config_json
+from .model_config import ConfigError, read_config_json
 from .registry import (
     Architecture,
     architecture_of,
@@ -14,7 +14,6 @@ __all__ = [
     "Architecture",
     "ConfigError",
     "EngineConfig",
-    "Qwen3Config",
     "architecture_of",
     "get_architecture",
     "known_architectures",

@@ -23,11 +23,14 @@
 #include <cuda.h>
 #include <string.h>
 
+#include <mutex>
+
 namespace cib {
 
 constexpr int kDecWarps = 4;
 constexpr int kDecStages = 3;
 constexpr int kDecKeys = 16;   // keys per warp block
+constexpr int kMaxDevices = 64;  // per-device set-up (shared-memory limit, address of the built-in scratch) is kept for this many
 
 template <int D>
 struct DecodeSmem {
@@ -92,116 +95,20 @@ __device__ __forceinline__ void load_block(__nv_bfloat16* sK, __nv_bfloat16* sV,
     }
 }
 
-// Optional fusion of the step before attention into this kernel: the rows are then the raw output of the q/k/v
-// projection, and the kernel itself applies the per-head RMSNorm and the rotary encoding to the group's queries
-// and to this step's key, writes that key and the value into the cache (the CTA whose key range holds the new
-// position does), and uses them from shared memory.  qkv == nullptr: the rows are finished queries and the cache
-// already holds the new token (csrc/qk_rope.cu ran before).
-struct DecodeFuse {
-    const __nv_bfloat16* qkv; int qkv_stride;
-    const int* positions; const int* slot_mapping;
-    AnyVec q_weight, k_weight; int has_norm; float eps;
-    const float* rope_table; int rotary_dim; int max_positions;
-    __nv_bfloat16* cache_w;
-};
-
-// One head of D values: optional RMSNorm, optional rotate-half encoding over the first `rot` values, rounded once.
-__device__ __forceinline__ void norm_rope_head(const __nv_bfloat16* src, float* scratch, const AnyVec& w, int has_norm,
-                                               float eps, const float* tab, int rot, int D, __nv_bfloat16* dst_smem,
-                                               __nv_bfloat16* dst_global, int lane) {
-    float ss = 0.f;
-    for (int i = lane; i < D; i += 32) {
-        const float x = __bfloat162float(src[i]);
-        scratch[i] = x;
-        ss += x * x;
-    }
-    if (has_norm) {
-        ss = warp_sum(ss);
-        const float factor = rsqrtf(ss / (float)D + eps);
-        for (int i = lane; i < D; i += 32) scratch[i] = scratch[i] * factor * w[i];
-    }
-    __syncwarp();
-    const int half = rot >> 1;
-    for (int i = lane; i < half; i += 32) {
-        const float c = tab[2 * i], sn = tab[2 * i + 1];
-        const float a = scratch[i], b = scratch[i + half];
-        const __nv_bfloat16 ra = __float2bfloat16_rn(a * c - b * sn), rb = __float2bfloat16_rn(b * c + a * sn);
-        dst_smem[i] = ra; dst_smem[i + half] = rb;
-        if (dst_global) { dst_global[i] = ra; dst_global[i + half] = rb; }
-    }
-    for (int i = rot + lane; i < D; i += 32) {
-        const __nv_bfloat16 v = __float2bfloat16_rn(scratch[i]);
-        dst_smem[i] = v;
-        if (dst_global) dst_global[i] = v;
-    }
-    __syncwarp();
-}
-
-// The same for the common case that the encoding spans the whole head (or is absent): every lane owns D / 32
-// neighbouring values, all loads are independent of each other (one memory latency), the partner of a rotation
-// pair sits 16 lanes away.
-template <int D>
-__device__ __forceinline__ void norm_rope_head_fast(const __nv_bfloat16* src, const AnyVec& w, int has_norm, float eps,
-                                                    const float* tab, __nv_bfloat16* dst_smem, __nv_bfloat16* dst_global,
-                                                    int lane) {
-    constexpr int E = D / 32;
-    float x[E], wv[E], cs[2 * E];
-#pragma unroll
-    for (int e = 0; e < E; ++e) x[e] = __bfloat162float(src[lane * E + e]);
-    if (has_norm) {
-#pragma unroll
-        for (int e = 0; e < E; ++e) wv[e] = w[lane * E + e];
-    }
-    if (tab) {
-        const float* tp = tab + 2 * ((lane & 15) * E);
-#pragma unroll
-        for (int e = 0; e < 2 * E; ++e) cs[e] = tp[e];
-    }
-    if (has_norm) {
-        float ss = 0.f;
-#pragma unroll
-        for (int e = 0; e < E; ++e) ss += x[e] * x[e];
-        ss = warp_sum(ss);
-        const float factor = rsqrtf(ss / (float)D + eps);
-#pragma unroll
-        for (int e = 0; e < E; ++e) x[e] = x[e] * factor * wv[e];
-    }
-    if (tab) {
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
-            const float c = cs[2 * e], sn = cs[2 * e + 1];
-            x[e] = lane < 16 ? x[e] * c - other * sn : x[e] * c + other * sn;
-        }
-    }
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-        const __nv_bfloat16 v = __float2bfloat16_rn(x[e]);
-        dst_smem[lane * E + e] = v;
-        if (dst_global) dst_global[lane * E + e] = v;
-    }
-}
-
-template <int D, bool FUSED, bool TMA>
+template <int D, bool TMA>
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                               int out_stride, const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
                               const int* __restrict__ block_table, int table_stride,
                               const int* __restrict__ seq_lens, int nq, int nkv, float scale_log2, int window,
                               int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                              int* __restrict__ counters, const DecodeFuse f, const __grid_constant__ CUtensorMap kv_map,
+                              int* __restrict__ counters, const __grid_constant__ CUtensorMap kv_map,
                               int* __restrict__ error_flag, const void* __restrict__ warm, unsigned long long warm_bytes) {
-    static_assert(!(FUSED && TMA), "the folded-in step writes rows of the cp.async layout");
     extern __shared__ __align__(128) unsigned char smem_unaligned[];
     // TMA writes whole 1024-byte swizzle atoms: the rings then start on such a boundary
     unsigned char* smem_raw = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023))
                                   : smem_unaligned;
     __shared__ uint64_t s_full[kDecWarps * kDecStages];          // TMA: bytes of a ring stage have landed
-    constexpr bool fused = FUSED;
-    // behind the rings: finished queries [16][D], this step's key and value [2][D], a 32-bit row per warp
-    __nv_bfloat16* s_q = reinterpret_cast<__nv_bfloat16*>(smem_raw + DecodeSmem<D>::kTotal);
-    __nv_bfloat16* s_new = s_q + 16 * D;
-    float* s_scratch = reinterpret_cast<float*>(s_new + 2 * D);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
     const int g = nq / nkv;
@@ -268,7 +175,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 #pragma unroll
     for (int s = 0; s < kDecStages - 1; ++s) {
         if (s < my_blocks) {
-            if (!fused && block_key(s) + kDecKeys > pos) deferred = s;
+            if (block_key(s) + kDecKeys > pos) deferred = s;
             else if (TMA) tma_block(s, block_key(s));
             else load_block<D>(stage_k(s), stage_v(s), cache, table, block_key(s), k_end, page_size, num_pages, nkv, kvh, lane);
         }
@@ -288,56 +195,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
     // ---- query fragments: rows 0..g-1 are the heads of this kv head, the rest are zero ----
     uint32_t qf[D / 16][4];
-    if (fused) {
-        // a decode step's token sits at position seq_len - 1
-        const int p = pos < 0 ? 0 : (f.max_positions > 0 && pos >= f.max_positions ? f.max_positions - 1 : pos);
-        const float* tab = f.rotary_dim > 0 ? f.rope_table + (size_t)p * (f.rotary_dim >> 1) * 2 : nullptr;
-        const bool whole_head = f.rotary_dim == 0 || f.rotary_dim == D;
-        const __nv_bfloat16* row = f.qkv + (size_t)r * f.qkv_stride;
-        float* scratch = s_scratch + warp * D;
-        const bool owns_new = pos >= k_begin && pos < k_end;
-        const int items = g + (owns_new ? 2 : 0);
-        for (int it = warp; it < items; it += kDecWarps) {
-            if (it < g) {
-                if (whole_head)
-                    norm_rope_head_fast<D>(row + (size_t)(kvh * g + it) * D, f.q_weight, f.has_norm, f.eps, tab, s_q + it * D, nullptr, lane);
-                else
-                    norm_rope_head(row + (size_t)(kvh * g + it) * D, scratch, f.q_weight, f.has_norm, f.eps, tab, f.rotary_dim, D,
-                                   s_q + it * D, nullptr, lane);
-            } else {
-                // this step's key (normed, encoded) or value (as it is): to the cache page and to shared memory
-                const bool is_k = it == g;
-                const int slot = f.slot_mapping[r];
-                __nv_bfloat16* dst = nullptr;
-                if (slot >= 0) {
-                    const int page = slot / page_size, off = slot - page * page_size;
-                    if (page < num_pages)
-                        dst = f.cache_w + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * D;
-                }
-                const __nv_bfloat16* src = row + (size_t)(nq + (is_k ? 0 : nkv) + kvh) * D;
-                if (is_k) {
-                    if (whole_head) norm_rope_head_fast<D>(src, f.k_weight, f.has_norm, f.eps, tab, s_new, dst, lane);
-                    else norm_rope_head(src, scratch, f.k_weight, f.has_norm, f.eps, tab, f.rotary_dim, D, s_new, dst, lane);
-                } else {
-                    for (int i = lane; i < D; i += 32) {
-                        const __nv_bfloat16 v = src[i];
-                        s_new[D + i] = v;
-                        if (dst) dst[i] = v;
-                    }
-                }
-            }
-        }
-        for (int i = threadIdx.x; i < (16 - g) * D; i += blockDim.x) s_q[g * D + i] = __float2bfloat16_rn(0.f);
-        __syncthreads();
-#pragma unroll
-        for (int kt = 0; kt < D / 16; ++kt) {
-            const int c0 = kt * 16 + quad * 2;
-            qf[kt][0] = *reinterpret_cast<const uint32_t*>(s_q + qrow * D + c0);
-            qf[kt][1] = *reinterpret_cast<const uint32_t*>(s_q + (qrow + 8) * D + c0);
-            qf[kt][2] = *reinterpret_cast<const uint32_t*>(s_q + qrow * D + c0 + 8);
-            qf[kt][3] = *reinterpret_cast<const uint32_t*>(s_q + (qrow + 8) * D + c0 + 8);
-        }
-    } else {
+    {
         const __nv_bfloat16* qp = q + (size_t)r * q_stride + (size_t)kvh * g * D;
 #pragma unroll
         for (int kt = 0; kt < D / 16; ++kt) {
@@ -382,17 +240,6 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(sV) + block_off<D, true>(idx / (D / 8), idx % (D / 8))) = make_uint4(0, 0, 0, 0);
             __syncwarp();
         }
-        if (fused && pos >= key0 && pos < key0 + kDecKeys) {
-            // the page row of this step's token was copied as the cache had it: put the fresh key and value there
-            const int prow = pos - key0;
-            if (lane < D / 8) {
-                const int sw = (lane ^ (prow & 7)) * 8;
-                *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(sK) + prow * D + sw) = *reinterpret_cast<const uint4*>(s_new + lane * 8);
-                *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(sV) + prow * D + sw) = *reinterpret_cast<const uint4*>(s_new + D + lane * 8);
-            }
-            __syncwarp();
-        }
-
         // ---- S = Q K^T for 16 keys ----
         float s[2][4];
 #pragma unroll
@@ -579,51 +426,53 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                          int page_size, const int* block_table, int table_stride, const int* seq_lens,
                          int num_requests, int nq, int nkv, float scale, int window, int splits, float* part_o,
                          float* part_ml, int* counters, cudaStream_t stream, bool use_pdl = false,
-                         const DecodeFuse* fuse = nullptr, int* error_flag = nullptr, const void* warm = nullptr,
-                         unsigned long long warm_bytes = 0) {
+                         int* error_flag = nullptr, const void* warm = nullptr, unsigned long long warm_bytes = 0) {
     const int g = nq / nkv;
-    DecodeFuse f;
-    if (fuse) f = *fuse;
-    else { f = DecodeFuse(); f.qkv = nullptr; f.q_weight = AnyVec{nullptr, 0}; f.k_weight = AnyVec{nullptr, 0}; }
     // TMA needs whole 16-slot blocks inside a page, blocks that start at multiples of 16 (no window), 64-column
     // panels, a place to report a wait that ran out, and row coordinates that fit 32 bits
     const long long total_rows = (long long)num_pages * 2 * nkv * page_size;
-    const bool tma = !fuse && error_flag != nullptr && page_size % kDecKeys == 0 && window <= 0 && D % 64 == 0 &&
+    const bool tma = error_flag != nullptr && page_size % kDecKeys == 0 && window <= 0 && D % 64 == 0 &&
                      total_rows < (1ll << 31) && ((uintptr_t)cache % 16) == 0;
     CUtensorMap kv_map;
     memset(&kv_map, 0, sizeof(kv_map));
     if (tma && encode_tensor_map_bf16_2d(&kv_map, cache, (unsigned long long)total_rows, D, D, 64, kDecKeys,
                                          "paged_attention_decode") != 0)
         return -1;
-    // rings, then the finished queries, the new key/value and one 32-bit row per warp
-    // (only when the step before is folded in: the extra bytes keep the next kernel's CTAs off the SM otherwise)
-    size_t smem = DecodeSmem<D>::kTotal + (fuse ? (size_t)(16 + 2) * D * 2 + (size_t)kDecWarps * D * 4 : 0) + (tma ? 1024 : 0);
+    size_t smem = DecodeSmem<D>::kTotal + (tma ? 1024 : 0);
     size_t merge = (size_t)(2 * kDecWarps * 16 + kDecWarps * g * D) * sizeof(float) + (tma ? 1024 : 0);
     const size_t combine = (size_t)(g * splits + g) * sizeof(float) + (tma ? 1024 : 0);
     if (combine > merge) merge = combine;
     if (merge > smem) smem = merge;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
-        if (e != cudaSuccess) {
-            set_error("paged_attention_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
+    // the larger shared-memory limit is a property of the kernel on one device: set once per device
+    {
+        static std::mutex mutex;
+        static bool configured[kMaxDevices] = {false};
+        int dev = -1;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+            set_error("paged_attention_decode: cannot tell the current device (%s)", cudaGetErrorString(e));
             return -2;
         }
-        configured = true;
+        std::lock_guard<std::mutex> lock(mutex);
+        if (!configured[dev]) {
+            e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+            if (e != cudaSuccess) {
+                set_error("paged_attention_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
+                return -2;
+            }
+            configured[dev] = true;
+        }
     }
     CIB_REQUIRE(smem <= 225 * 1024, "paged_attention_decode: needs %zu bytes of shared memory", smem);
     dim3 grid(splits, nkv, num_requests);
     const float scale_log2 = scale * 1.4426950408889634f;
-    auto kernel = fuse ? paged_attention_decode_kernel<D, true, false>
-                       : (tma ? paged_attention_decode_kernel<D, false, true> : paged_attention_decode_kernel<D, false, false>);
+    auto kernel = tma ? paged_attention_decode_kernel<D, true> : paged_attention_decode_kernel<D, false>;
     cudaError_t e = launch_pdl(kernel, grid, dim3(kDecWarps * 32), smem, stream, use_pdl,
                                (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                                (const __nv_bfloat16*)cache, num_pages, page_size, block_table, table_stride, seq_lens, nq,
-                               nkv, scale_log2, window, splits, part_o, part_ml, counters, f, kv_map, error_flag, warm, warm_bytes);
+                               nkv, scale_log2, window, splits, part_o, part_ml, counters, kv_map, error_flag, warm, warm_bytes);
     if (e != cudaSuccess) {
         set_error("paged_attention_decode: launch failed: %s", cudaGetErrorString(e));
         return -2;
@@ -670,47 +519,9 @@ extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out
     if (((uintptr_t)warm % 16) != 0 || warm_bytes <= 0) { warm = nullptr; warm_bytes = 0; }
     const unsigned long long wb = (unsigned long long)warm_bytes;
     switch (head_dim) {
-        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag, warm, wb);
-        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag, warm, wb);
-        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, nullptr, error_flag, warm, wb);
-    }
-    return -1;
-}
-
-// The same kernel with the step before it folded in: `qkv` holds the raw rows of the q/k/v projection
-// ([q heads | k heads | v heads] x head_dim, row stride qkv_stride); the kernel norms (if has_norm) and encodes
-// (if rotary_dim > 0) the queries and this step's key, and writes key and value to `cache` at slot_mapping[r]
-// (slot < 0: no write).  Replaces cib_qk_norm_rope_kv_write + cib_paged_attention_decode for decode steps.
-extern "C" int cib_paged_attention_decode_fused(const void* qkv, int qkv_stride, void* out, int out_stride, void* cache,
-                                                int num_pages, int page_size, const int* block_table, int table_stride,
-                                                const int* seq_lens, const int* positions, const int* slot_mapping,
-                                                const void* q_weight, const void* k_weight, int weight_dtype, int has_norm,
-                                                float eps, const float* rope_table, int rotary_dim, int max_positions,
-                                                int num_requests, int nq, int nkv, int head_dim, float scale, int window,
-                                                int splits, float* scratch, int* counters, int use_pdl, cudaStream_t stream) {
-    CIB_REQUIRE(cib_paged_attention_decode_supports(head_dim, nq, nkv),
-                "paged_attention_decode_fused: head_dim %d with %d/%d heads is not taken by this kernel", head_dim, nq, nkv);
-    CIB_REQUIRE(num_requests >= 0 && splits >= 1 && splits <= 128, "paged_attention_decode_fused: bad sizes R=%d splits=%d", num_requests, splits);
-    CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0, "paged_attention_decode_fused: bad cache geometry");
-    CIB_REQUIRE(qkv_stride >= (nq + 2 * nkv) * head_dim && qkv_stride % 2 == 0, "paged_attention_decode_fused: row stride %d too small", qkv_stride);
-    CIB_REQUIRE(positions && slot_mapping, "paged_attention_decode_fused: positions and slot mapping are needed");
-    CIB_REQUIRE(!has_norm || (q_weight && k_weight), "paged_attention_decode_fused: norm weights missing");
-    CIB_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0 && (rotary_dim == 0 || (rope_table && max_positions > 0)),
-                "paged_attention_decode_fused: bad rotary arguments");
-    CIB_REQUIRE(splits == 1 || (scratch && counters), "paged_attention_decode_fused: splits need scratch and counters");
-    CIB_REQUIRE(num_requests <= 65535 && nkv <= 65535, "paged_attention_decode_fused: grid too large");
-    if (num_requests == 0) return 0;
-    DecodeFuse f;
-    f.qkv = (const __nv_bfloat16*)qkv; f.qkv_stride = qkv_stride; f.positions = positions; f.slot_mapping = slot_mapping;
-    f.q_weight = AnyVec{q_weight, weight_dtype == kBF16}; f.k_weight = AnyVec{k_weight, weight_dtype == kBF16};
-    f.has_norm = has_norm; f.eps = eps; f.rope_table = rope_table; f.rotary_dim = rotary_dim; f.max_positions = max_positions;
-    f.cache_w = (__nv_bfloat16*)cache;
-    float* part_o = scratch;
-    float* part_ml = scratch ? scratch + (size_t)num_requests * nq * splits * head_dim : nullptr;
-    switch (head_dim) {
-        case 64: return launch_decode<64>(qkv, qkv_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, &f);
-        case 128: return launch_decode<128>(qkv, qkv_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, &f);
-        case 256: return launch_decode<256>(qkv, qkv_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, &f);
+        case 64: return launch_decode<64>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, error_flag, warm, wb);
+        case 128: return launch_decode<128>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, error_flag, warm, wb);
+        case 256: return launch_decode<256>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, seq_lens, num_requests, nq, nkv, scale, window, splits, part_o, part_ml, counters, stream, use_pdl != 0, error_flag, warm, wb);
     }
     return -1;
 }
@@ -718,15 +529,12 @@ extern "C" int cib_paged_attention_decode_fused(const void* qkv, int qkv_stride,
 // ---- the variant that allocates nothing (see attention_decode_static.h) --------------------------------------
 #include "attention_decode_static.h"
 
-#include <mutex>
-
 namespace cib {
 
 // Partial results of the splits, then the counters (as ints) behind them.  In host code this name is only a
 // stand-in for the symbol; the device address is looked up once per device below.
 static __device__ __align__(256) float g_static_decode_scratch[kStaticScratchFloats + kStaticCounters];
 
-constexpr int kMaxDevices = 64;
 static float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
 static std::mutex g_static_scratch_mutex;
 

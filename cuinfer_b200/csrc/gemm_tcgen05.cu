@@ -203,9 +203,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
                             const float g = __uint_as_float(gv[8 * j + e]), u = __uint_as_float(uv[8 * j + e]);
-                            // the hardware's exponential and reciprocal (2 ulp): far below the bfloat16 rounding of
-                            // the result, and the exact ones would make the epilogue longer than the tile's MMAs
-                            y[e] = __fdividef(g, 1.f + __expf(-g)) * u;
+                            // exact exponential and division, as in every other place the gate is computed: the same
+                            // activation must not round differently with the number of rows in the step
+                            y[e] = g / (1.f + expf(-g)) * u;
                         }
                         uint4 pk;
                         __nv_bfloat162 t0 = __floats2bfloat162_rn(y[0], y[1]), t1 = __floats2bfloat162_rn(y[2], y[3]);

@@ -224,6 +224,9 @@ argmax_cluster_kernel(const float* __restrict__ logits, int ld, int vocab, int* 
     const int row = blockIdx.x / kArgmaxCtas, rank = (int)cluster.block_rank();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = logits + (size_t)row * ld;
+    // Distributed shared memory may only be touched once every CTA of the cluster runs: arrive here, wait before the
+    // remote store, so that the scan hides the barrier.
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     const int chunk = ((vocab + kArgmaxCtas - 1) / kArgmaxCtas + 3) & ~3;
     const int begin = min(vocab, rank * chunk), end = min(vocab, begin + chunk);
     float best = -INFINITY;
@@ -245,6 +248,7 @@ argmax_cluster_kernel(const float* __restrict__ logits, int ld, int vocab, int* 
     for (int o = 16; o > 0; o >>= 1)
         take_better(best, best_i, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, best_i, o));
     if (lane == 0) { s_val[warp] = best; s_idx[warp] = best_i; }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
         best = lane < kArgmaxThreads / 32 ? s_val[lane] : -INFINITY;
@@ -252,6 +256,7 @@ argmax_cluster_kernel(const float* __restrict__ logits, int ld, int vocab, int* 
         for (int o = 16; o > 0; o >>= 1)
             take_better(best, best_i, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, best_i, o));
         if (lane == 0) {
+            // every CTA of the cluster has started (the barrier above the scan): its shared memory may be written
             *cluster.map_shared_rank(&s_part_val[rank], 0) = best;
             *cluster.map_shared_rank(&s_part_idx[rank], 0) = best_i;
         }

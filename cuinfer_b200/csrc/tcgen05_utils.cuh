@@ -30,10 +30,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: false if the limit was hit (the caller raises the error flag and leaves).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit_cycles = kTcWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
-    while (clock64() - start < kTcWaitCycles) {
+    while (clock64() - start < limit_cycles) {
         if (mbar_try_wait(bar, parity)) return true;
     }
     return false;

@@ -40,7 +40,7 @@ class EngineCore:
     def __init__(self, config: EngineConfig) -> None:
         self.config = config
         self.runner = ModelRunner(config.model_path, config)
-        eos = getattr(self.runner.model_config, "eos_token_ids", ())
+        eos = self.runner.spec.eos_token_ids
         self.scheduler = Scheduler(
             self.runner.manager, max_num_seqs=config.max_num_seqs,
             max_num_scheduled_tokens=config.max_num_scheduled_tokens,

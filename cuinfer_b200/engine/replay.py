@@ -27,15 +27,19 @@ from .runner import ModelRunner, StepEntry
 TRACE_TOKEN_ROUNDING = 64
 
 
-def make_runner(model_dir: str, dtype: str, max_tokens: int, block_size: int = 16, max_live: int = 8) -> ModelRunner:
-    """A runner whose page pool holds exactly ``max_tokens`` tokens (rounded up to whole pages)."""
+def make_runner(model_dir: str, dtype: str, max_tokens: int, block_size: int = 16, max_live: int = 8,
+                cuda_graph: bool = False) -> ModelRunner:
+    """A runner whose page pool holds exactly ``max_tokens`` tokens (rounded up to whole pages).
+    ``cuda_graph``: steps go the way generation sends them — a step of single tokens that all want their logits
+    through ``ModelRunner.decode_step`` (one CUDA graph per bucket of rows and class of context length), a
+    prompt-sized step whose shape has been seen before through its captured graph; default: every step eagerly."""
     if max_tokens <= 0:
         raise ValueError("--max-tokens must be positive")
     unit = max(TRACE_TOKEN_ROUNDING, block_size)
     rounded = (max_tokens + unit - 1) // unit * unit
     pages = (rounded + block_size - 1) // block_size
     config = EngineConfig(model_path=model_dir, block_size=block_size, dtype=dtype, num_blocks=pages,
-                          max_num_seqs=max_live, max_num_scheduled_tokens=1 << 30, enable_cuda_graph=False)
+                          max_num_seqs=max_live, max_num_scheduled_tokens=1 << 30, enable_cuda_graph=cuda_graph)
     return ModelRunner(model_dir, config)
 
 
@@ -60,7 +64,10 @@ def run_trace(runner: ModelRunner, lines, out_dir: str, log=sys.stdout) -> int:
                     raise SystemExit(
                         f"trace_run: step {step_id}: no room for {len(e.tokens)} more tokens of request {e.request_id!r} "
                         f"({runner.manager.num_free_pages()} pages of {runner.page_size} tokens free); --max-tokens is too small")
-            logits = runner.step(entries)
+            if runner.can_use_graph(entries) and all(list(e.want) == [0] for e in entries):
+                logits = runner.decode_step(entries)
+            else:
+                logits = runner.step(entries)
             if logits.shape[0]:
                 host = logits.float().cpu().contiguous().numpy().astype("<f4", copy=False)
                 kernels.check_error_flags()
@@ -81,8 +88,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
+    parser.add_argument("--graphs", action="store_true",
+                        help="run decode steps and repeated prompt shapes from CUDA graphs, as generation does")
     args = parser.parse_args(argv)
-    runner = make_runner(args.model, args.dtype, args.max_tokens, args.block_size)
+    runner = make_runner(args.model, args.dtype, args.max_tokens, args.block_size, cuda_graph=args.graphs)
     run_trace(runner, sys.stdin, args.out)
     return 0
 

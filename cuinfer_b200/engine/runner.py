@@ -139,14 +139,8 @@ class ModelRunner:
         return int(pages)
 
     def _activation_bytes(self) -> int:
-        t = self.config.max_num_scheduled_tokens
-        widest = 0
-        for layer in self.spec.layers:
-            inter = layer.feed_forward.get("intermediate_size", 0) or 0
-            heads = (layer.mixer.get("num_heads", 0) or 0) + 2 * (layer.mixer.get("num_kv_heads", 0) or 0)
-            widest = max(widest, 3 * inter, 2 * heads * (layer.mixer.get("head_dim", 0) or 0))
-        width = 2 if self.dtype == torch.bfloat16 else 4
-        return t * (widest * width + 3 * self.spec.hidden_size * 4) + self.config.max_num_seqs * self.vocab_size * 8
+        """What a step of a full token budget allocates beside weights and cache; the parts say how much."""
+        return self.model.workspace_bytes(self.config.max_num_scheduled_tokens, self.config.max_num_seqs)
 
     # ---- requests ------------------------------------------------------------------------------------
     def reserve(self, request_id: Hashable, num_new_tokens: int) -> bool:
@@ -338,7 +332,7 @@ class ModelRunner:
     STEP_GRAPH_LIMIT = 4
 
     def _step_graph(self, entries: Sequence[StepEntry]) -> Optional["StepGraph"]:
-        if not self.config.enable_cuda_graph or len(entries) > self.STEP_GRAPH_MAX_ENTRIES:
+        if not self.config.enable_cuda_graph or len(entries) > self.STEP_GRAPH_MAX_ENTRIES or not self.model.capturable:
             return None
         lens = tuple(len(e.tokens) for e in entries)
         if sum(lens) < self.STEP_GRAPH_MIN_TOKENS:
@@ -381,7 +375,7 @@ class ModelRunner:
     GRAPH_CONTEXTS = (512, 2048, 8192, 32768, 131072)
 
     def can_use_graph(self, entries: Sequence[StepEntry]) -> bool:
-        return (self.config.enable_cuda_graph and len(entries) <= self.GRAPH_BUCKETS[-1]
+        return (self.config.enable_cuda_graph and self.model.capturable and len(entries) <= self.GRAPH_BUCKETS[-1]
                 and all(len(e.tokens) == 1 for e in entries))
 
     def decode_graph(self, rows: int, longest: Optional[int] = None) -> "DecodeGraph":
@@ -486,6 +480,7 @@ class DecodeGraph:
         self._view(host, "qsl")[:] = np.arange(B + 1, dtype=np.int32)
         self._view(host, "want")[:] = np.arange(B, dtype=np.int32)
         self._view(host, "sl")[:] = 1
+        self._view(host, "slots")[:] = -1
         for g in range(len(self.runner.groups)):       # padding rows never write to the cache
             self._view(host, f"sm{g}")[:] = -1
             self._view(host, f"bt{g}")[:] = -1
@@ -498,8 +493,8 @@ class DecodeGraph:
         ctx = StepContext(
             num_tokens=B, num_requests=B, token_ids=self._dev("tok"), positions=self._dev("pos"),
             token_request=self._dev("treq"), query_start_loc=self._dev("qsl"), seq_lens=self._dev("sl"),
-            state_slots=self._dev("slots"), query_start_loc_host=list(range(B + 1)), seq_lens_host=[],
-            state_slots_host=[], max_query_len=1, max_seq_len=self.context, groups=groups, decode_only=True)
+            state_slots=self._dev("slots"), query_start_loc_host=list(range(B + 1)), seq_lens_host=None,
+            state_slots_host=None, max_query_len=1, max_seq_len=self.context, groups=groups, decode_only=True)
         for run, (src, writes) in r._run_cache.items():
             ctx.kv[run] = PagedKV(r.storage.run_cache[src], groups[r.storage.run_group[src]], writes)
         ctx.state = r.storage.state
@@ -530,9 +525,10 @@ class DecodeGraph:
         sl[:n] = np.asarray(starts, dtype=np.int32) + 1
         sl[n:] = 1
         slots[:n] = [mgr.slot(e.request_id) for e in entries]
-        slots[n:] = 0
+        slots[n:] = -1          # padding rows own no state
         # Block-table rows change rarely (a page every page_size steps): each staging buffer remembers which
-        # request and how many pages every row holds, and only new entries are written.
+        # admission (the manager's serial, not the caller's id: an id may come back with other pages) and how many
+        # pages every row holds, and only new entries are written.
         state = self.row_state[i]
         for g in range(len(r.groups)):
             sm = self._view(host, f"sm{g}")
@@ -549,13 +545,14 @@ class DecodeGraph:
                 if k > P:
                     raise StepError(f"request {e.request_id!r} holds {k} pages, more than the graph's table stride {P}")
                 known = state[g][row]
-                if not windowed and known is not None and known[0] == e.request_id and known[1] <= k:
+                serial = mgr.serial(e.request_id)
+                if not windowed and known is not None and known[0] == serial and known[1] <= k:
                     if known[1] < k:
                         bt[row, known[1]:k] = table[known[1]:k]
                 else:
                     bt[row, :k] = table
                     bt[row, k:] = -1
-                state[g][row] = (e.request_id, k)
+                state[g][row] = (serial, k)
                 page = table[start // ps]
                 if page < 0:
                     raise StepError(f"request {e.request_id!r}: its new token has no page in group {g}")
@@ -619,6 +616,10 @@ class StepGraph:
         if runner is None:
             raise RuntimeError("the engine of this step graph is gone")
         ctx, want = runner.build_context(entries, table_stride=self.stride, arena=self.arena)
+        # what a replay cannot know: only the query lengths (the graph's key) stay on the host side of the context
+        ctx.seq_lens_host = None
+        ctx.state_slots_host = None
+        ctx.max_seq_len = runner.max_model_len
         if self.graph is not None:
             self.graph.replay()
             kernels.note_flagged_launch(replayed=True)

@@ -72,8 +72,6 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
         "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _P, ctypes.c_longlong, _P],
         "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-        "cib_paged_attention_decode_fused": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I,
-                                             _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P],
         "cib_attention_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
         "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "cib_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -81,6 +79,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_gemm_generic": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
         "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
         "cib_argmax_rows": [_P, _I, _I, _I, _P, _P],
+        "cib_selftest_bounded_wait": [ctypes.c_longlong, _P, _P, _P],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -354,56 +353,6 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
     _count()
 
 
-def _decode_scratch(q: torch.Tensor, R: int, num_q_heads: int, num_kv_heads: int, head_dim: int, splits: int):
-    if splits <= 1:
-        return None, None
-    n = library().cib_paged_attention_decode_scratch_floats(R, num_q_heads, head_dim, splits)
-    scratch = torch.empty(n, dtype=torch.float32, device=q.device)
-    need = R * num_kv_heads
-    counters = _decode_counters.get(q.device.index)
-    if counters is None or counters.numel() < need:
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("paged_attention_decode: the split counters must exist before a graph capture "
-                              "(run the step once eagerly first)")
-        if counters is not None:
-            _retired.append(counters)
-        counters = torch.zeros(max(need, 4096), dtype=torch.int32, device=q.device)
-        _decode_counters[q.device.index] = counters
-    return scratch, counters
-
-
-def paged_attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
-                                 seq_lens: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor,
-                                 q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
-                                 rope_table: torch.Tensor | None, rotary_dim: int, num_q_heads: int, num_kv_heads: int,
-                                 head_dim: int, scale: float, window: int, splits: int) -> None:
-    """Decode attention straight from the raw q/k/v rows: per-head norm, rotary encoding and the cache write of
-    this step's token happen inside the attention kernel (no separate kernel before it)."""
-    R = qkv.shape[0]
-    if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
-        raise KernelError("paged_attention_decode_fused: bfloat16 only")
-    if qkv.stride(1) != 1 or out.stride(1) != 1 or out.shape != (R, num_q_heads * head_dim):
-        raise KernelError("paged_attention_decode_fused: rows must be dense and out [R, nq*d]")
-    has_norm = q_weight is not None
-    if has_norm and (k_weight is None or k_weight.dtype != q_weight.dtype):
-        raise KernelError("paged_attention_decode_fused: q and k norm weights must both be given, in one dtype")
-    scratch, counters = _decode_scratch(qkv, R, num_q_heads, num_kv_heads, head_dim, splits)
-    rc = library().cib_paged_attention_decode_fused(
-        _cuda(qkv, "qkv", contiguous=False), qkv.stride(0), _cuda(out, "out", contiguous=False), out.stride(0),
-        _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
-        block_table.stride(0), _cuda(seq_lens, "seq_lens", torch.int32), _cuda(positions, "positions", torch.int32),
-        _cuda(slot_mapping, "slot_mapping", torch.int32),
-        _cuda(q_weight, "q_weight") if has_norm else None, _cuda(k_weight, "k_weight") if has_norm else None,
-        _code(q_weight, "q_weight") if has_norm else 0, 1 if has_norm else 0, float(eps),
-        _cuda(rope_table, "rope_table", torch.float32) if rope_table is not None else None,
-        rotary_dim if rope_table is not None else 0, rope_table.shape[0] if rope_table is not None else 0,
-        R, num_q_heads, num_kv_heads, head_dim, float(scale), int(window), int(splits),
-        scratch.data_ptr() if scratch is not None else None, counters.data_ptr() if counters is not None else None,
-        1 if use_pdl else 0, _stream())
-    _check(rc, "paged_attention_decode_fused")
-    _count()
-
-
 def paged_attention_prefill_supports(head_dim: int, num_q_heads: int, num_kv_heads: int) -> bool:
     return bool(library().cib_paged_attention_prefill_supports(head_dim, num_q_heads, num_kv_heads))
 
@@ -562,6 +511,19 @@ def check_error_flags(force: bool = False) -> None:
         if code:
             flag.zero_()
             raise KernelError(f"a kernel on cuda:{index} gave up waiting on a barrier (code {code}); its results are invalid")
+
+
+def selftest_bounded_wait(limit_cycles: int = 1_000_000, device: torch.device | str = "cuda:0",
+                          gave_up: torch.Tensor | None = None) -> None:
+    """Run the kernels' bounded mbarrier wait on a barrier that never completes (it gives up after ``limit_cycles``
+    and raises the device's error word); the next ``check_error_flags`` must then raise.  For tests of the failure
+    path: a healthy kernel never takes it."""
+    device = torch.device(device)
+    rc = library().cib_selftest_bounded_wait(int(limit_cycles), _error_flag(device).data_ptr(),
+                                             _cuda(gave_up, "gave_up", torch.int32) if gave_up is not None else None, _stream())
+    _check(rc, "selftest_bounded_wait")
+    note_flagged_launch()
+    _count()
 
 
 def attention_tcgen05_supports(head_dim: int, num_q_heads: int, num_kv_heads: int, page_size: int) -> bool:

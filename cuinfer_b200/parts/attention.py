@@ -12,7 +12,6 @@ position=PartSpec(...))``; ``scale`` None means ``head_dim ** -0.5``; ``window``
 """
 from __future__ import annotations
 
-import os
 from typing import List, Optional
 
 import torch
@@ -24,13 +23,6 @@ from .context import StepContext
 from .linear import Linear
 from .registry import MIXERS, POSITION_ENCODINGS
 from .spec import PagedCacheNeed, PartSpec, TensorSpec
-
-
-# Decode steps can fold the per-head norm, the encoding and the cache write of the new token into the attention
-# kernel (one kernel fewer per layer).  Measured on the Qwen3-0.6B shape at batch 8 it is slower than the separate
-# kernel chained by programmatic dependent launch (1.83 ms against 1.69 ms per step: every attention CTA then
-# waits for the projection and repeats the query work), so it is off unless CUINFER_B200_FUSED_DECODE=1.
-FUSED_DECODE = os.environ.get("CUINFER_B200_FUSED_DECODE", "0") == "1"
 
 
 @MIXERS.register("attention")
@@ -93,20 +85,18 @@ class PagedAttention(Mixer):
     def cache_need(self) -> Optional[PagedCacheNeed]:
         return PagedCacheNeed(self.num_kv_heads, self.head_dim, self.window or None)
 
+    @property
+    def capturable(self) -> bool:
+        return self.position.capturable
+
+    def workspace_bytes(self, tokens: int) -> int:
+        # q/k/v rows, the attention output, the projection's output
+        width = 2 if self.dtype == torch.bfloat16 else 4
+        return self.qkv.workspace_bytes(tokens) + tokens * self.q_size * width + self.o.workspace_bytes(tokens)
+
     def forward(self, x: torch.Tensor, ctx: StepContext, run: int) -> torch.Tensor:
         kv = ctx.paged_kv(run)
         qkv = self.qkv.forward(x)
-        if (FUSED_DECODE and ctx.decode_only and kv.writes and qkv.dtype == torch.bfloat16
-                and kernels.paged_attention_decode_supports(self.head_dim, self.num_heads, self.num_kv_heads)):
-            # decode steps: norm, encoding and the cache write of the new token happen inside the attention kernel
-            out = torch.empty((qkv.shape[0], self.q_size), dtype=qkv.dtype, device=qkv.device)
-            splits = kernels.decode_splits(ctx.num_requests, self.num_kv_heads, max(1, ctx.max_seq_len))
-            kernels.paged_attention_decode_fused(
-                qkv, out, kv.cache, kv.group.block_table, ctx.seq_lens, ctx.positions, kv.group.slot_mapping,
-                self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps, self.position.table(),
-                self.position.rotary_dim, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
-                splits)
-            return self.o.forward(out)
         kernels.qk_norm_rope_kv_write(
             qkv, ctx.positions, kv.group.slot_mapping if kv.writes else None,
             self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps,

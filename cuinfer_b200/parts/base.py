@@ -76,11 +76,24 @@ class LazyNorm:
 
 
 class Part:
+    # Whether the part's ``forward`` may be recorded into a CUDA graph and replayed for other batches: it reads the
+    # batch from the device arrays of the context only, launches the same kernels whatever the batch holds, and never
+    # waits for the device.  A part that loops over ``ctx.seq_lens_host`` / ``ctx.state_slots_host``, sizes a launch from
+    # values of the batch, or synchronises says False here; a model with such a part runs every step eagerly, with the
+    # host arrays of the context filled in.  Under a capture those two host arrays are None, so that a part that reads
+    # them without having said so fails at once instead of replaying another batch's values.
+    capturable: bool = True
+
     def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
         self.spec = spec
         self.hidden_size = hidden_size
         self.prefix = prefix
         self.dtype = dtype
+
+    def workspace_bytes(self, tokens: int) -> int:
+        """Device memory the part's ``forward`` allocates for intermediate results of a step of ``tokens`` rows (its
+        output included).  The engine leaves this much free when it sizes the cache pool from the device's memory."""
+        return 0
 
     def tensors(self) -> List[TensorSpec]:
         return []
@@ -105,6 +118,14 @@ class Norm(Part):
 
     def norm_rows(self, rows: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
+
+    def fusable_rms(self) -> Optional[tuple]:
+        """``(gain, eps)`` if this norm is exactly ``x * rsqrt(mean(x^2) + eps) * gain`` over the whole row, so that a
+        projection may compute it in its own kernel; None (the default) keeps the norm a kernel of its own."""
+        return None
+
+    def workspace_bytes(self, tokens: int) -> int:
+        return tokens * self.hidden_size * (2 if self.dtype == torch.bfloat16 else 4)
 
 
 class PositionEncoding(Part):
@@ -139,11 +160,17 @@ class Block:
         self.feed_forward = feed_forward
         self.prefix = prefix
 
+    capturable: bool = True          # as Part.capturable, for what the arrangement itself does
+
     def parts(self) -> List[Part]:
         raise NotImplementedError
 
     def forward(self, stream: ResidualStream, ctx: StepContext, run: int) -> None:
         raise NotImplementedError
+
+    def workspace_bytes(self, tokens: int) -> int:
+        """Largest sum of intermediate results alive at one time in the block (see Part.workspace_bytes)."""
+        return sum(part.workspace_bytes(tokens) for part in self.parts())
 
     # hints for the L2 (see Part): the weight the layer reads first, and the weight that follows the layer
     def first_weight(self) -> Optional[torch.Tensor]:

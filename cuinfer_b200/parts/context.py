@@ -45,10 +45,13 @@ class StepContext:
     query_start_loc: torch.Tensor    # [R + 1] int32
     seq_lens: torch.Tensor           # [R] int32, tokens each request holds after this step
     state_slots: torch.Tensor        # [R] int32, the fixed-size state slot of each request
-    # host copies of the small arrays, for parts that decide launches on the host
+    # Host copies of the small arrays, for parts that decide launches on the host.  ``query_start_loc_host`` is always
+    # there (a captured step is keyed by its query lengths).  The other two are None while a step is captured into a
+    # CUDA graph or replayed: only a part that declares ``capturable = False`` may read them (the model then runs
+    # eagerly).  In a decode graph, rows beyond the live requests are padding: state slot -1, empty block table.
     query_start_loc_host: List[int] = field(default_factory=list)
-    seq_lens_host: List[int] = field(default_factory=list)
-    state_slots_host: List[int] = field(default_factory=list)
+    seq_lens_host: Optional[List[int]] = field(default_factory=list)
+    state_slots_host: Optional[List[int]] = field(default_factory=list)
     max_query_len: int = 0
     max_seq_len: int = 0
     groups: Dict[int, GroupView] = field(default_factory=dict)

@@ -44,6 +44,9 @@ class SwiGLU(FeedForward):
     def warm_after(self, weight: Optional[torch.Tensor]) -> None:
         self.down.warm_next = weight
 
+    def workspace_bytes(self, tokens: int) -> int:
+        return self.gate_up.workspace_bytes(tokens, silu_pair=True) + self.down.workspace_bytes(tokens)
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = self.gate_up.forward(x, silu_pair=True)       # silu(gate) * up, fused where the kernel allows
         return self.down.forward(act)

@@ -56,6 +56,13 @@ class Linear:
         if self.weight.dtype != self.dtype:
             self.weight = self.weight.to(self.dtype)
 
+    def workspace_bytes(self, tokens: int, silu_pair: bool = False) -> int:
+        """Bytes of the projection's output for ``tokens`` rows (with ``silu_pair`` the stacked product may exist
+        beside the gated one)."""
+        width = 2 if self.dtype == torch.bfloat16 else 4
+        n = sum(self.out_features)
+        return tokens * (n + n // 2 if silu_pair else n) * width
+
     def tie(self, weight: torch.Tensor) -> None:
         """Use another tensor's storage as this projection's weight (a tied output head)."""
         if tuple(weight.shape) != (sum(self.out_features), self.in_features):
@@ -110,15 +117,15 @@ class Linear:
             kernels.gemm_wstream(rows, w, out, silu_pair=True)
             return out
         if lazy and x._rows is None:
-            from .norm import RMSNorm
-            norm, stream = x.norm, x.stream
-            if (type(norm) is RMSNorm and norm.weight is not None and stream.residual.is_contiguous()
+            stream = x.stream
+            rms = x.norm.fusable_rms()
+            if (rms is not None and stream.residual.is_contiguous()
                     and K <= gemm_dispatch.FUSED_NORM_MAX_K and kernels.gemm_skinny_supports(M, N, K, True)
                     and (stream.pending is None or stream.pending.is_contiguous())):
                 out = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
                 has_delta = stream.pending is not None
-                kernels.gemm_skinny(w, out, residual=stream.residual, pending=stream.pending, norm_weight=norm.weight,
-                                    eps=norm.eps, residual_out=stream.spare() if has_delta else None, silu_pair=silu_pair,
+                kernels.gemm_skinny(w, out, residual=stream.residual, pending=stream.pending, norm_weight=rms[0],
+                                    eps=rms[1], residual_out=stream.spare() if has_delta else None, silu_pair=silu_pair,
                                     warm=self.warm_next)
                 if has_delta:
                     stream.swap()

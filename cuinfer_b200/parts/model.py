@@ -123,6 +123,21 @@ class DecoderModel:
                 out[run] = need
         return out
 
+    # ---- what the engine asks before it runs the model -----------------------------------------------
+    @property
+    def capturable(self) -> bool:
+        """True when every part's and block's ``forward`` may be replayed from a CUDA graph (Part.capturable)."""
+        return all(block.capturable for block in self.blocks) and all(part.capturable for part in self.parts())
+
+    def workspace_bytes(self, tokens: int, rows: int) -> int:
+        """Device memory a step of ``tokens`` rows with ``rows`` wanted logits needs beside weights and cache: the
+        32-bit residual stream with its spare and a pending delta, the widest block's intermediate results, and the
+        wanted rows with their logits (twice: the sampler works on a copy)."""
+        residual = 3 * tokens * self.hidden_size * 4
+        widest = max((block.workspace_bytes(tokens) for block in self.blocks), default=0)
+        head = rows * (self.hidden_size * 8 + self.vocab_size * 8)
+        return residual + widest + head
+
     # ---- compute -------------------------------------------------------------------------------------
     def forward(self, ctx: StepContext) -> ResidualStream:
         residual = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=ctx.token_ids.device)

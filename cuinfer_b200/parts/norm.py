@@ -27,6 +27,9 @@ class RMSNorm(Norm):
     def load(self, store) -> None:
         self.weight = store.get(self.tensors()[0])
 
+    def fusable_rms(self):
+        return (self.weight, self.eps) if self.weight is not None else None
+
     def add_norm(self, stream: ResidualStream) -> torch.Tensor:
         out = torch.empty(stream.residual.shape, dtype=self.dtype, device=stream.residual.device)
         kernels.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out)

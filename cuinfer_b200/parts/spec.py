@@ -94,6 +94,7 @@ class ModelSpec:
     lm_head_name: str | None = "lm_head.weight"   # None: the output head is the embedding table
     order: tuple[int, ...] | None = None
     cache_source: Mapping[int, int] = field(default_factory=dict)
+    eos_token_ids: tuple[int, ...] = ()           # sampling one of these ends a request (unless it ignores them)
 
     def run_order(self) -> tuple[int, ...]:
         order = self.order if self.order is not None else tuple(range(len(self.layers)))
@@ -120,6 +121,7 @@ class TensorSpec:
     name: str
     shape: tuple[int, ...]
     keep_stored_precision: bool = False
+    integer: bool = False    # an integer table (kept as int32); a floating tensor in its place is refused, and vice versa
     init: str = "normal"     # how the random-weights mode fills it: "normal" or "ones" (a gain)
 
 

@@ -4,7 +4,8 @@ The reference looks each tensor up by its exact name with an expected dtype and 
 at the first problem ("missing checkpoint tensor", "mismatched dtype/shape",
 csrc/model/checkpoint.cpp:142-158).  Here the model first hands over its whole list of expected
 tensors; :meth:`WeightStore.check` compares it with the checkpoint and raises ONE error that
-lists every missing tensor, every unexpected tensor and every wrong shape.
+lists every missing tensor, every unexpected tensor and every wrong shape or kind of dtype (an integer
+tensor where a floating one is expected, or the other way round).
 
 Precision rule: on a bfloat16 engine floating tensors are kept in bfloat16, except that a tensor
 marked ``keep_stored_precision`` that the file stores in 32 bits stays in 32 bits; integer tables
@@ -43,8 +44,9 @@ class WeightStore:
                 got = self.checkpoint.entry(name).shape
                 if tuple(got) != tuple(spec.shape):
                     wrong.append(f"{name}: expected {list(spec.shape)}, got {list(got)}")
-                elif not (self.checkpoint.entry(name).dtype.is_floating_point or not _is_float_role(spec)):
-                    wrong.append(f"{name}: expected a floating dtype, got {self.checkpoint.entry(name).dtype}")
+                elif self.checkpoint.entry(name).dtype.is_floating_point == spec.integer:
+                    wrong.append(f"{name}: expected {'an integer' if spec.integer else 'a floating'} dtype, "
+                                 f"got {self.checkpoint.entry(name).dtype}")
         if missing or unexpected or wrong:
             lines = [f"failed to load checkpoint {self.model_dir}: the tensors do not fit the model"]
             if missing:
@@ -52,7 +54,7 @@ class WeightStore:
             if unexpected:
                 lines.append(f"  unexpected ({len(unexpected)}): " + ", ".join(sorted(unexpected)))
             if wrong:
-                lines.append(f"  wrong shape ({len(wrong)}): " + "; ".join(sorted(wrong)))
+                lines.append(f"  wrong shape or dtype ({len(wrong)}): " + "; ".join(sorted(wrong)))
             raise WeightError("\n".join(lines))
         self._expected = expected
 
@@ -90,7 +92,3 @@ class WeightStore:
 
     def close(self) -> None:
         self.checkpoint.close()
-
-
-def _is_float_role(spec: TensorSpec) -> bool:
-    return True

@@ -61,8 +61,17 @@ class SafetensorsFile:
         (header_len,) = struct.unpack("<Q", self._fh.read(8))
         if header_len == 0 or header_len > _MAX_HEADER or 8 + header_len > size:
             raise WeightError(f"invalid safetensors header size {header_len} in {path} (file has {size} bytes)")
+        def no_duplicates(pairs):
+            # a name that occurs twice in the header is an error (csrc/model/checkpoint.cpp:121-124), not "the last wins"
+            out = {}
+            for key, value in pairs:
+                if key in out:
+                    raise WeightError(f"duplicate tensor '{key}' in the header of {path}")
+                out[key] = value
+            return out
+
         try:
-            header = json.loads(self._fh.read(header_len).decode("utf-8"))
+            header = json.loads(self._fh.read(header_len).decode("utf-8"), object_pairs_hook=no_duplicates)
         except (UnicodeDecodeError, json.JSONDecodeError) as exc:
             raise WeightError(f"invalid safetensors header in {path}: {exc}") from exc
         if not isinstance(header, dict):

@@ -9,7 +9,8 @@ import pytest
 import torch
 
 from conftest import TINY_A, TINY_B
-from cuinfer_b200.config import (ConfigError, EngineConfig, Qwen3Config, get_architecture, known_architectures,
+from cuinfer_b200.models.qwen3 import Qwen3Config
+from cuinfer_b200.config import (ConfigError, EngineConfig, get_architecture, known_architectures,
                                  load_model_config, register_architecture, unregister_architecture)
 from cuinfer_b200.parts import DecoderModel
 from cuinfer_b200.weights import Checkpoint, WeightError, WeightStore, write_random_model, write_safetensors
@@ -152,6 +153,7 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     del tensors["model.layers.0.self_attn.q_norm.weight"]
     tensors["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(64)
     tensors["model.layers.1.self_attn.k_proj.weight"] = torch.zeros(48, 64)
+    tensors["model.layers.1.self_attn.v_proj.weight"] = torch.zeros(32, 64, dtype=torch.int32)   # right shape, integers
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
     store = _store(folder)
     with pytest.raises(WeightError) as err:
@@ -159,7 +161,14 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     msg = str(err.value)
     assert "missing (2)" in msg and "model.layers.1.mlp.down_proj.weight" in msg and "q_norm.weight" in msg
     assert "unexpected (1)" in msg and "q_proj.bias" in msg
-    assert "wrong shape (1)" in msg and "k_proj.weight: expected [32, 64], got [48, 64]" in msg
+    assert "wrong shape or dtype (2)" in msg and "k_proj.weight: expected [32, 64], got [48, 64]" in msg
+    assert "v_proj.weight: expected a floating dtype, got torch.int32" in msg
+    # and the other way round: a part that asks for an integer table refuses a floating tensor in its place
+    from cuinfer_b200.parts.spec import TensorSpec
+    with pytest.raises(WeightError, match="model.norm.weight: expected an integer dtype, got torch.float32"):
+        _store(folder).check([TensorSpec("model.norm.weight", (64,), integer=True)] +
+                             [TensorSpec(n, tuple(t.shape), integer=not t.is_floating_point) for n, t in tensors.items()
+                              if n != "model.norm.weight"])
 
 
 @pytest.mark.parametrize("damage, word", [
@@ -188,6 +197,12 @@ def test_bad_offsets_dtype_and_missing_file(tmp_path):
         Checkpoint(str(tmp_path))
     with pytest.raises(WeightError, match="cannot open"):
         Checkpoint(str(tmp_path / "nowhere"))
+    # the same name twice in a header: an error (csrc/model/checkpoint.cpp:121-124), not "the last one wins"
+    entry = '{"dtype": "F32", "shape": [2], "data_offsets": [%d, %d]}'
+    blob = ('{"x": ' + entry % (0, 8) + ', "y": ' + entry % (8, 16) + ', "x": ' + entry % (8, 16) + '}').encode()
+    (tmp_path / "model.safetensors").write_bytes(struct.pack("<Q", len(blob)) + blob + b"\0" * 16)
+    with pytest.raises(WeightError, match="duplicate tensor 'x'"):
+        Checkpoint(str(tmp_path))
 
 
 def test_sharded_checkpoint(tmp_path):

@@ -323,3 +323,54 @@ def test_random_workloads_do_not_depend_on_engine_settings(model_folders):
                 else:
                     assert got[rid] == want[rid] and reasons.get(rid) == want_reasons.get(rid), (seed, options, rid)
     assert preempted > 0 and ahead > 0
+
+
+def _drive(engine, wanted_ids):
+    """Step the engine until the requests ``wanted_ids`` are gone; returns their tokens."""
+    out = {rid: [] for rid in wanted_ids}
+    guard = 0
+    while any(rid in engine.scheduler.requests for rid in wanted_ids):
+        for o in engine.step():
+            if o.request_id in out:
+                out[o.request_id].extend(o.new_token_ids)
+        guard += 1
+        assert guard < 2000
+    return out
+
+
+@pytest.mark.parametrize("live", [1, 2])
+def test_request_id_that_comes_back_gets_its_own_pages(model_folders, live):
+    """A caller's request id may be used again after the request has ended (a conversation id).  The second
+    request lands in the same row of the same decode graph with at least as many pages, from other places of the
+    pool: the block-table rows that the graph keeps on the device must be written anew, or its attention reads the
+    first request's pages.  Also after an abort.  Graphs on, float32, against the plain implementation."""
+    from cuinfer_b200 import SamplingParams
+    from cuinfer_b200.config import EngineConfig
+    from cuinfer_b200.engine.core import EngineCore
+
+    folders, cfg, block = model_folders["A"]
+    folder = folders["float32"]
+    pcfg, weights = plain_qwen3.load_folder(folder)
+    engine = EngineCore(EngineConfig(model_path=folder, dtype="float32", block_size=block, num_blocks=40,
+                                     max_num_seqs=4, max_num_scheduled_tokens=256, enable_cuda_graph=True))
+    params = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    ids = ["x", "y"][:live]
+    lengths = [[20, 37], [41, 40], [52, 49]]              # each round at least as many pages as the round before
+    for round_no, lens in enumerate(lengths):
+        prompts = {rid: random_tokens(cfg["vocab_size"], lens[i], 900 + 10 * round_no + i) for i, rid in enumerate(ids)}
+        for rid in ids:
+            engine.add_request(rid, prompts[rid], params)
+        if round_no == 1:
+            # abort in the middle of decoding, then the same ids once more with the same prompts
+            for _ in range(8):
+                engine.step()
+            engine.abort(ids)
+            while engine.has_requests():
+                engine.step()
+            for rid in ids:
+                engine.add_request(rid, prompts[rid], params)
+        got = _drive(engine, ids)
+        for rid in ids:
+            assert got[rid] == plain_qwen3.greedy_generate(pcfg, weights, prompts[rid], 24), (round_no, rid)
+    assert engine.runner.graph_steps > 40
+    engine.runner.manager.check()

@@ -485,46 +485,6 @@ def test_paged_attention_prefill(nq, nkv, d, ps, window):
     close(out, attention_reference(case, lens, new, scale, window), 1.5e-2)
 
 
-@pytest.mark.parametrize("nq, nkv, d, ps, rot, norm", [(16, 8, 128, 16, 128, True), (8, 2, 64, 32, 32, True),
-                                                          (12, 3, 128, 5, 0, False), (4, 4, 64, 16, 64, False)])
-@pytest.mark.parametrize("splits", [1, 4])
-def test_paged_attention_decode_fused_equals_the_two_kernels(nq, nkv, d, ps, rot, norm, splits):
-    """The attention kernel with norm, encoding and cache write folded in gives what the separate kernel before it
-    plus the plain attention kernel give, and leaves the same cache behind."""
-    k = _k()
-    lens = [1, 2, 16, 17, 64, 333, 1000]
-    R = len(lens)
-    case = attention_case(torch.bfloat16, nq, nkv, d, lens, [1] * R, ps, seed=70)
-    cache0, bt = case["cache"].to(DEV), case["bt"].to(DEV)
-    qkv = rand(R, (nq + 2 * nkv) * d, seed=71, dtype=torch.bfloat16).to(DEV)
-    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
-    slots = torch.tensor([int(bt[r, (n - 1) // ps]) * ps + (n - 1) % ps for r, n in enumerate(lens)], dtype=torch.int32, device=DEV)
-    slots[2] = -1                                     # a padding row writes nothing
-    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
-    qw = (1 + rand(d, seed=72, scale=0.3)).to(torch.bfloat16).to(DEV) if norm else None
-    kw = (1 + rand(d, seed=73, scale=0.3)).to(torch.bfloat16).to(DEV) if norm else None
-    table = None
-    if rot:
-        inv = 1.0 / torch.pow(torch.tensor(10000.0), torch.arange(rot // 2, dtype=torch.float32) * 2.0 / rot)
-        ang = torch.arange(1100, dtype=torch.float32)[:, None] * inv[None, :]
-        table = torch.stack((torch.cos(ang), torch.sin(ang)), -1).contiguous().to(DEV)
-    scale = 1.0 / math.sqrt(d)
-    # the two kernels
-    cache_a, rows_a = cache0.clone(), qkv.clone()
-    k.qk_norm_rope_kv_write(rows_a, positions, slots, qw, kw, 1e-5, table, rot, cache_a, nq, nkv, d)
-    want = torch.empty(R, nq * d, dtype=torch.bfloat16, device=DEV)
-    k.paged_attention_decode(rows_a, want, cache_a, bt, sl, nq, nkv, d, scale, 0, splits)
-    # the fused kernel
-    cache_b = cache0.clone()
-    got = torch.full_like(want, 5.0)
-    for _ in range(2):
-        k.paged_attention_decode_fused(qkv, got, cache_b, bt, sl, positions, slots, qw, kw, 1e-5, table, rot, nq, nkv, d,
-                                       scale, 0, splits)
-    rows = [r for r in range(R) if r != 2]            # row 2 has no slot: the two-kernel path reads a stale key there
-    assert torch.equal(got[rows].cpu(), want[rows].cpu())
-    assert torch.equal(cache_b.cpu(), cache_a.cpu())
-
-
 @pytest.mark.parametrize("nq, nkv, ps", [(16, 8, 16), (8, 1, 32), (4, 4, 8), (32, 2, 128), (2, 1, 256)])
 @pytest.mark.parametrize("window", [None, 200])
 def test_attention_tcgen05(nq, nkv, ps, window):
@@ -615,3 +575,62 @@ def test_argmax_rows(V, ld):
     want = [P.sample_plain(torch.nan_to_num(logits[i], nan=-float("inf")), 0.0, 0, 1.0, 0.5) for i in range(rows)]
     assert got == want and got[1] == V // 2 and got[2] == 0 and got[3] == V - 1 and got[4] == 0
     assert got == _sample(k, logits.contiguous(), [(0.0, 0, 1.0, 0.5)] * rows)
+
+
+# ---- the failure path of the bounded waits --------------------------------------------------------------
+
+def test_bounded_wait_that_runs_out_raises_the_error_word():
+    """Every TMA / tcgen05 kernel waits on its mbarriers with a limit and raises the device's error word when the
+    limit is reached; ``check_error_flags`` turns the word into an exception.  No healthy run takes that path, so a
+    self-test kernel takes it harmlessly: it waits, with the kernels' own loop and a short limit, on a barrier that
+    nothing arrives on, then gives up and returns.  The exception must come after a plain launch, and after a replay
+    of a CUDA graph that holds the launch (the engine reads the word only now and then for replayed steps)."""
+    k = _k()
+    k.check_error_flags(force=True)                       # start clean
+    gave_up = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k.selftest_bounded_wait(1_000_000, DEV, gave_up)
+    with pytest.raises(k.KernelError, match="gave up waiting on a barrier \\(code 91\\)"):
+        k.check_error_flags()
+    assert int(gave_up.item()) == 1
+    k.check_error_flags(force=True)                       # the word was cleared: nothing is raised twice
+    # the same inside a captured graph; the word is read when a check is forced
+    gave_up.zero_()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        k.selftest_bounded_wait(500_000, DEV, gave_up)
+    k.check_error_flags(force=True)                       # capturing ran nothing
+    assert int(gave_up.item()) == 0
+    graph.replay()
+    k.note_flagged_launch(replayed=True)
+    k.check_error_flags()                                 # one replayed step: not looked at yet
+    with pytest.raises(k.KernelError, match="code 91"):
+        k.check_error_flags(force=True)
+    assert int(gave_up.item()) == 1
+    # a limit beyond what the self-test allows is refused on the host, nothing is launched
+    with pytest.raises(k.KernelError, match="the limit must be between"):
+        k.selftest_bounded_wait(10**12, DEV)
+    k.check_error_flags(force=True)
+
+
+def test_gated_epilogues_agree_on_large_gates():
+    """silu(g) * u with gates far out (|g| up to ~200, where exp(-g) overflows 32 bits): the prompt-sized tcgen05
+    kernel, the weight-streaming kernel and the few-rows kernel give the exact formula's value, none a NaN."""
+    k = _k()
+    K, I = 64, 128
+    x = torch.zeros(128, K, dtype=torch.bfloat16)
+    x[:, 0] = 1.0
+    w = torch.zeros(2 * I, K, dtype=torch.bfloat16)
+    gates = torch.linspace(-200.0, 200.0, I)
+    w[:I, 0] = gates.to(torch.bfloat16)
+    w[I:, 0] = 1.5
+    g = w[:I, 0].float()
+    want = (g / (1 + torch.exp(-g)) * 1.5).expand(128, I)
+    for M, fn in [(128, k.gemm_tcgen05), (128, k.gemm_wstream), (8, None)]:
+        out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        if fn is None:
+            k.gemm_skinny(w.to(DEV), out, act=x[:M].to(DEV), silu_pair=True)
+        else:
+            fn(x[:M].to(DEV), w.to(DEV), out, silu_pair=True)
+        assert bool(torch.isfinite(out.float()).all())
+        close(out, want[:M], 4e-3)

@@ -171,6 +171,8 @@ def _define_toy_mixer():
     class RunningMean(Mixer):
         """y_t = W · mean(x_0 .. x_t).  Per-request state: the running sum of x and the count, 32-bit."""
 
+        capturable = False      # loops over the batch's state slots on the host: never replayed from a CUDA graph
+
         def tensors(self):
             return [TensorSpec(f"{self.prefix}.proj.weight", (self.hidden_size, self.hidden_size))]
 
@@ -260,6 +262,8 @@ def _define_toy_routed_parts():
         @FEED_FORWARDS.register("toy_routed")
         class ToyRouted(FeedForward):
             """y = sum over a token's top-k experts of softmax-weight x relu(x W_in^T) W_out^T; router in 32 bits."""
+
+            capturable = False      # sizes its expert products from the routing (torch.nonzero waits for the device)
 
             def tensors(self):
                 e, w, h = self.spec.experts, self.spec.width, self.hidden_size
@@ -387,6 +391,48 @@ def _routing_margin(cfg, w, ids):
     gaps = []
     _routed_plain(cfg, w, ids, gaps)
     return min(gaps)
+
+
+# ---- 4b. the toy architectures through the entry point, with the engine's default settings --------------------------
+
+def _plain_greedy(plain_fn, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(torch.argmax(plain_fn(ids)[-1])))
+    return ids[len(prompt):]
+
+
+@pytest.mark.parametrize("arch", ["window", "twice", "state", "routed"])
+def test_toy_architectures_generate_with_default_settings(arch, tmp_path):
+    """``LLM.generate`` with CUDA graphs and run-ahead on (the defaults) on models made of other parts: the windowed
+    and the cache-sharing attention are replayed from decode graphs; the toy mixer with state and the routed toy
+    feed-forward say ``capturable = False`` and the engine runs their steps eagerly, host arrays filled in.  Greedy
+    float32 tokens equal the plain restatement's in every case."""
+    from cuinfer_b200 import LLM, SamplingParams
+    from cuinfer_b200.weights import write_random_model
+
+    name, spec_fn, plain, extra = {
+        "window": ("ToyWindowLM", _window_spec, _window_plain, dict(theta=5000.0, eps=1e-5)),
+        "twice": ("ToyTwiceLM", _twice_spec, _twice_plain, dict(theta=10000.0, eps=1e-6)),
+        "state": ("ToyStateLM", _toy_spec, _toy_plain, dict(theta=10000.0, eps=1e-6)),
+        "routed": ("ToyRoutedLM", _routed_spec, _routed_plain, dict(eps=3e-6)),
+    }[arch]
+    _register(name, spec_fn)
+    cfg = _base_cfg(name, **extra)
+    folder = write_random_model(str(tmp_path / "m"), cfg, 11, std=0.08, gain_std=0.1, dtype="float32")
+    pcfg, w = P.load_folder(folder)
+    prompts = [random_tokens(V, n, 800 + i) for i, n in enumerate([30, 7, 52, 19, 3])]
+    llm = LLM(folder, dtype="float32", num_blocks=48, max_num_seqs=8)          # everything else as it comes
+    assert llm.config.enable_cuda_graph and llm.config.decode_run_ahead
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=26, ignore_eos=True))
+    for prompt, res in zip(prompts, out):
+        assert res.token_ids == _plain_greedy(lambda ids: plain(pcfg, w, ids), prompt, 26), (arch, len(prompt))
+    runner = llm.engine.runner
+    capturable = arch in ("window", "twice")
+    assert runner.model.capturable == capturable
+    assert (runner.graph_steps > 20) == capturable          # graphs where the parts allow them, eager steps elsewhere
+    runner.manager.check()
+    assert not runner.manager.live_requests()
 
 
 # ---- 5. single parts against their formulas ---------------------------------------------------------------------------

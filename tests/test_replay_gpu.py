@@ -103,6 +103,103 @@ def test_decode_through_tma_and_long_prompts(model_folders, tmp_path, monkeypatc
     _run(model_folders, "D", "bfloat16", steps, requests, tmp_path, max_tokens=traces.live_token_peak(steps))
 
 
+CUTS = {
+    "whole": (lambda r: traces.whole(r), [1, 5, 17, 33, 100, 161]),
+    "tail": (lambda r: traces.tail_decode(r, 32), [40, 97, 130]),
+    "portions": (lambda r: traces.portions(r), [64, 131, 90]),
+    "mixed": (lambda r: traces.mixed(r, max_live=4), [70, 33, 120, 58, 90, 45, 101]),
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("cut", sorted(CUTS))
+def test_cuts_through_cuda_graphs(model_folders, name, dtype, cut, tmp_path, monkeypatch):
+    """The four cuts again, through the paths generation really takes: every step of single tokens is a replayed
+    decode graph (padding rows, incremental block-table upload), every other step whose shape has come back is a
+    replayed step graph.  The trace runs three times through one runner — shapes are captured the second time and
+    replayed the third — and the logits of the last pass are compared, at the same tolerance as eager steps."""
+    from cuinfer_b200.engine.runner import ModelRunner
+    monkeypatch.setattr(ModelRunner, "STEP_GRAPH_MIN_TOKENS", 2)
+    monkeypatch.setattr(ModelRunner, "STEP_GRAPH_LIMIT", 64)
+    folders, cfg, block = model_folders[name]
+    folder = folders[dtype]
+    build, lengths = CUTS[cut]
+    requests = _requests(cfg, lengths, seed=11)
+    steps = build(requests)
+    out = str(tmp_path / "out")
+    runner = traces.replay_in_process(folder, dtype, steps, out, traces.live_token_peak(steps), block,
+                                      cuda_graph=True, passes=3)
+    got = traces.collect(steps, out, cfg["vocab_size"])
+    traces.compare_with_plain(folder, requests, got, TOLERANCE[dtype])
+    decode_steps = sum(all(len(e["tokens"]) == 1 and e["want"] == [0] for e in st["entries"]) for st in steps)
+    assert runner.graph_steps == 3 * decode_steps
+    other = len(steps) - decode_steps
+    shapes = {tuple((len(e["tokens"]), len(e["want"])) for e in st["entries"]) for st in steps
+              if not all(len(e["tokens"]) == 1 and e["want"] == [0] for e in st["entries"])}
+    # pass 1 runs every such step eagerly, pass 2 captures each shape at its first return, pass 3 replays everything
+    assert runner.step_graph_replays >= other and len(runner._step_graphs) == len(shapes)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_graph_buckets_and_padding_rows(model_folders, dtype, tmp_path):
+    """Decode steps with 17, 9 and 3 live requests: graphs for 24, 12 and 4 rows with 7, 3 and 1 padding rows, the
+    rows of requests that ended cleared for those that move up.  Logits of every step against the plain model."""
+    folders, cfg, block = model_folders["B"]
+    folder = folders[dtype]
+    requests = _requests(cfg, [20 + 3 * i for i in range(17)], seed=12)
+    ids = list(requests)
+    steps, s, done = [], 0, {}
+    for rid in ids:                                  # prompts, one request a step, all but the last 12 tokens
+        head = len(requests[rid]) - 12
+        steps.append({"step": s, "entries": [{"id": rid, "tokens": requests[rid][:head], "want": [head - 1]}], "end": []})
+        done[rid] = head
+        s += 1
+    live = list(ids)
+    for round_no in range(12):
+        entries = [{"id": r, "tokens": [requests[r][done[r]]], "want": [0]} for r in live]
+        for r in live:
+            done[r] += 1
+        leaving = []
+        if round_no == 3:
+            leaving = live[:8]                       # 9 stay and move up to rows 0..8
+        elif round_no == 7:
+            leaving = live[3:]                       # 3 stay
+        elif round_no == 11:
+            leaving = list(live)
+        steps.append({"step": s, "entries": entries, "end": leaving})
+        live = [r for r in live if r not in leaving]
+        s += 1
+    out = str(tmp_path / "out")
+    runner = traces.replay_in_process(folder, dtype, steps, out, traces.live_token_peak(steps), block,
+                                      cuda_graph=True, max_live=32)
+    assert sorted(b for b, _c in runner._graphs) == [4, 12, 24]
+    got = traces.collect(steps, out, cfg["vocab_size"])
+    import plain_qwen3
+    cfg_p, weights = plain_qwen3.load_folder(folder)
+    for rid, rows in got.items():
+        ref = plain_qwen3.forward(cfg_p, weights, list(requests[rid])).numpy()
+        scale = float(np.abs(ref).max())
+        for pos, row in rows.items():
+            err = float(np.abs(row - ref[pos]).max()) / scale
+            assert err <= TOLERANCE[dtype], (rid, pos, err)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_graph_across_context_classes(model_folders, dtype, tmp_path):
+    """A request that decodes from 500 to 530 tokens changes the class of context length its decode graph is
+    captured for (512 -> 2048): another graph, another split of the keys, the same logits."""
+    folders, cfg, block = model_folders["C"]
+    requests = _requests(cfg, [530, 140], seed=13)
+    steps = traces.tail_decode(requests, 30)
+    out = str(tmp_path / "out")
+    runner = traces.replay_in_process(folders[dtype], dtype, steps, out, traces.live_token_peak(steps), block,
+                                      cuda_graph=True)
+    assert sorted(c for _b, c in runner._graphs) == [512, min(2048, cfg["max_position_embeddings"])]
+    got = traces.collect(steps, out, cfg["vocab_size"])
+    traces.compare_with_plain(folders[dtype], requests, got, TOLERANCE[dtype])
+
+
 def test_trace_run_program(model_folders, tmp_path):
     """``bin/trace_run`` as a user calls it: lines on stdin, ``done`` lines back, files in --out, exit 0."""
     folders, cfg, block = model_folders["A"]

@@ -5,8 +5,10 @@ given all free device memory to the cache pool, or a C serving loop that must ke
 synchronise the whole device) out of its steps.  For them the split-key decode attention has a variant whose
 scratch lives in a fixed ``__device__`` array inside the library.  This test calls that variant through its
 exported C symbol, twice in a row with different inputs, and checks each result against the ordinary entry point
-(``cib_paged_attention_decode`` with a torch-allocated scratch) within the tolerance of the kernel tests.  It also
-checks that a call too large for the built-in array is refused.  The file sorts last so that a run that stops at
+(``cib_paged_attention_decode`` with a torch-allocated scratch) within the tolerance of the kernel tests, one of
+them also against a plain 32-bit attention on the CPU.  It checks what the entry point is for — the device's
+free memory and torch's own allocation count are the same before and after a call — and that a call too large for
+the built-in array is refused.  The file sorts last so that a run that stops at
 the first failure has already run every other test.
 """
 from __future__ import annotations
@@ -39,7 +41,7 @@ def _call(fn, q, out, cache, bt, sl, nq, nkv, d, scale, window, splits):
 
 def test_static_scratch_entry_point_matches_the_allocating_one():
     from cuinfer_b200 import kernels
-    from test_kernels_gpu import attention_case, close
+    from test_kernels_gpu import attention_case, attention_reference, close
 
     lib = kernels.library()
     fn = _entry(lib)
@@ -47,6 +49,8 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
     for seed, (nq, nkv, d, ps, splits, lens) in enumerate([
         (16, 8, 128, 16, 5, [1, 17, 64, 333, 1000, 2, 129, 640]),
         (8, 2, 64, 32, 3, [700, 3, 96]),
+        (4, 2, 256, 16, 1, [50, 301]),                 # one split: no partial results, head size 256
+        (6, 3, 256, 16, 4, [1, 200, 77]),
     ]):
         case = attention_case(torch.bfloat16, nq, nkv, d, lens, [1] * len(lens), ps, seed=50 + seed, sharp=True)
         q, cache, bt = case["wide"].to(DEV), case["cache"].to(DEV), case["bt"].to(DEV)
@@ -55,11 +59,20 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
         want = torch.empty(len(lens), nq * d, dtype=torch.bfloat16, device=DEV)
         kernels.paged_attention_decode(q, want, cache, bt, sl, nq, nkv, d, scale, 0, splits)
         got = torch.full_like(want, 3.0)
+        # the first launch of a kernel may load its code onto the device; after it a call allocates nothing
+        rc = _call(fn, q, got, cache, bt, sl, nq, nkv, d, scale, 0, splits)
+        assert rc == 0, lib.cib_last_error().decode()
+        got.fill_(3.0)
+        torch.cuda.synchronize()
+        free_before, allocated_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         rc = _call(fn, q, got, cache, bt, sl, nq, nkv, d, scale, 0, splits)
         assert rc == 0, lib.cib_last_error().decode()
         torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == allocated_before
         close(got, want, 1.5e-2)
         assert torch.equal(got.cpu(), want.cpu())          # same kernel, same inputs: the very same bits
+        if seed in (1, 2):  # and not only against itself: a plain 32-bit attention over the same cache
+            close(got, attention_reference(case, lens, [1] * len(lens), scale), 1.5e-2)
     # a call beyond the built-in array is refused with a message, and nothing is written
     R, nq, nkv, d, splits = 64, 16, 8, 128, 17
     assert R * nq * splits * (d + 2) > STATIC_SCRATCH_FLOATS

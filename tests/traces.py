@@ -140,14 +140,18 @@ def collect(steps: List[dict], out_dir: str, vocab: int) -> Dict[str, Dict[int, 
     return got
 
 
-def replay_in_process(model_dir: str, dtype: str, steps: List[dict], out_dir: str, max_tokens: int, block_size: int):
-    """Run a trace through ``cuinfer_b200.engine.replay`` in this process (same code as ``bin/trace_run``)."""
+def replay_in_process(model_dir: str, dtype: str, steps: List[dict], out_dir: str, max_tokens: int, block_size: int,
+                      cuda_graph: bool = False, passes: int = 1, max_live: int = 8):
+    """Run a trace through ``cuinfer_b200.engine.replay`` in this process (same code as ``bin/trace_run``).
+    ``passes``: run the whole trace this often through the same runner (a step shape is captured into a CUDA graph
+    only when it comes back); the files of the last pass stay."""
     from cuinfer_b200.engine import replay
 
-    runner = replay.make_runner(model_dir, dtype, max_tokens, block_size)
-    log = io.StringIO()
-    replay.run_trace(runner, to_lines(steps).splitlines(), out_dir, log=log)
-    assert log.getvalue().split() == [w for st in steps for w in ("done", str(st["step"]))]
+    runner = replay.make_runner(model_dir, dtype, max_tokens, block_size, max_live=max_live, cuda_graph=cuda_graph)
+    for _ in range(passes):
+        log = io.StringIO()
+        replay.run_trace(runner, to_lines(steps).splitlines(), out_dir, log=log)
+        assert log.getvalue().split() == [w for st in steps for w in ("done", str(st["step"]))]
     runner.manager.check()
     assert not runner.manager.live_requests(), "every request of the trace ended, so nothing may stay held"
     return runner
