@@ -68,6 +68,22 @@ TOLERANCE = {"float32": 5e-5, "bfloat16": 4e-2}
 GAINS = {"float32": {"q_norm": 3.0, "k_norm": 1.5}, "bfloat16": {"q_norm": 2.0, "k_norm": 1.0}}
 
 
+# The largest error every comparison with the plain implementation saw, per dtype; printed at the end of a run, so
+# that the bound can be kept close to what is measured.
+WORST_ERRORS = {}
+
+
+def note_error(dtype: str, where: str, err: float) -> None:
+    if err > WORST_ERRORS.get(dtype, ("", -1.0))[1]:
+        WORST_ERRORS[dtype] = (where, err)
+
+
+def pytest_terminal_summary(terminalreporter):
+    for dtype, (where, err) in sorted(WORST_ERRORS.items()):
+        terminalreporter.write_line(f"largest {dtype} error against the plain implementation: {err:.3e} of the largest "
+                                    f"logit ({where}); allowed {TOLERANCE[dtype]:.1e}")
+
+
 @pytest.fixture(scope="session")
 def model_folders(tmp_path_factory):
     """{name: ({dtype: folder}, config dict, block_size)}.  The float32 folder stores float32 weights, the

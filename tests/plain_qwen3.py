@@ -133,6 +133,18 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> torch.
     return x @ head.T
 
 
+def logits_at(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], positions: Sequence[int]) -> torch.Tensor:
+    """The rows ``positions`` of ``forward``'s result, with the output head applied to those rows only (for
+    vocabularies where the whole [n, vocab] matrix would be large)."""
+    x = embed(w["model.embed_tokens.weight"], ids)
+    pos = torch.arange(len(ids))
+    for i in range(cfg["num_hidden_layers"]):
+        x = decoder_layer(x, w, i, cfg, pos)
+    x = rms_norm(x[torch.tensor(list(positions), dtype=torch.long)], w["model.norm.weight"], cfg["rms_norm_eps"])
+    head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
+    return x @ head.T
+
+
 def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], num_new: int) -> List[int]:
     """Argmax decoding by recomputing the whole sequence each time; ties go to the lowest id
     (csrc/ops/sampler.cu:31-38)."""

@@ -53,6 +53,8 @@ def _replay_all(folder, dtype, requests, tmp_path, plain_fn, block=16):
                 err = float(np.abs(row - ref[pos]).max()) / scale
                 worst = max(worst, err)
                 assert err <= TOLERANCE[dtype], f"{label}: request {rid} first wrong position {pos} (error {err:.3e})"
+    from conftest import note_error
+    note_error(dtype, "toy parts", worst)
     return worst
 
 

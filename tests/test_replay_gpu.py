@@ -32,7 +32,7 @@ def _run(model_folders, name, dtype, steps, requests, tmp_path, max_tokens=None)
     peak = traces.live_token_peak(steps)
     runner = traces.replay_in_process(folder, dtype, steps, out, max_tokens or peak, block)
     got = traces.collect(steps, out, cfg["vocab_size"])
-    worst = traces.compare_with_plain(folder, requests, got, TOLERANCE[dtype])
+    worst = traces.compare_with_plain(folder, requests, got, TOLERANCE[dtype], label=f"replay of tiny {name}")
     return runner, worst
 
 
@@ -131,7 +131,7 @@ def test_cuts_through_cuda_graphs(model_folders, name, dtype, cut, tmp_path, mon
     runner = traces.replay_in_process(folder, dtype, steps, out, traces.live_token_peak(steps), block,
                                       cuda_graph=True, passes=3)
     got = traces.collect(steps, out, cfg["vocab_size"])
-    traces.compare_with_plain(folder, requests, got, TOLERANCE[dtype])
+    traces.compare_with_plain(folder, requests, got, TOLERANCE[dtype], label=f"graph replay {cut} of tiny {name}")
     decode_steps = sum(all(len(e["tokens"]) == 1 and e["want"] == [0] for e in st["entries"]) for st in steps)
     assert runner.graph_steps == 3 * decode_steps
     other = len(steps) - decode_steps

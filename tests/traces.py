@@ -157,7 +157,7 @@ def replay_in_process(model_dir: str, dtype: str, steps: List[dict], out_dir: st
     return runner
 
 
-def compare_with_plain(model_dir: str, requests: Dict[str, Sequence[int]], got, tolerance: float):
+def compare_with_plain(model_dir: str, requests: Dict[str, Sequence[int]], got, tolerance: float, label: str = ""):
     """Every collected row against the plain implementation's logits of the whole sequence.
     Returns the largest error seen, as a fraction of the largest plain logit of its sequence."""
     cfg, weights = plain_qwen3.load_folder(model_dir)
@@ -174,4 +174,7 @@ def compare_with_plain(model_dir: str, requests: Dict[str, Sequence[int]], got, 
             assert err <= tolerance, (
                 f"request {rid}: first wrong position {pos} of {len(toks)} (error {err:.3e} of the largest logit, "
                 f"allowed {tolerance:.1e})")
+    if label:
+        from conftest import note_error
+        note_error("float32" if tolerance < 1e-3 else "bfloat16", label, worst)
     return worst
