@@ -11,6 +11,9 @@
 // Modes:
 //   bench     B requests decode to --context tokens; K timed decode steps after W warm-up steps; then
 //             2048-token prompts one at a time (prefill).  Prints one JSON object.
+//   serve     the reference's own benchmark workload (benchmark.sh:67-97) without HTTP: prompts of --prompt-len random
+//             tokens, --max-tokens outputs, --batch requests in flight (a new one is added when one ends), 3 x batch
+//             requests timed after batch warm-up requests.  Prints one JSON object.
 //   generate  reads prompts (one line of space-separated ids each) from --prompts, generates --max-tokens
 //             greedy tokens for each and prints one line of ids per prompt (golden tokens for the tests).
 #include <algorithm>
@@ -54,6 +57,7 @@ struct Args
     int prefill_tokens = 2048;
     int prefill_runs = 5;
     int max_tokens = 16;
+    int prompt_len = 1024;
     int block_size = 16;
     int max_num_scheduled_tokens = 8192;
     int max_num_seqs = 256;
@@ -83,6 +87,7 @@ Args parse(int argc, char** argv)
         else if (k == "--prefill-tokens") a.prefill_tokens = std::stoi(next());
         else if (k == "--prefill-runs") a.prefill_runs = std::stoi(next());
         else if (k == "--max-tokens") a.max_tokens = std::stoi(next());
+        else if (k == "--prompt-len") a.prompt_len = std::stoi(next());
         else if (k == "--block-size") a.block_size = std::stoi(next());
         else if (k == "--max-num-scheduled-tokens") a.max_num_scheduled_tokens = std::stoi(next());
         else if (k == "--max-num-seqs") a.max_num_seqs = std::stoi(next());
@@ -278,6 +283,49 @@ int run_bench(const Args& a, const Config& config)
     return 0;
 }
 
+int run_serve(const Args& a, const Config& config)
+{
+    Engine engine(config);
+    const int vocab = engine.runner.model_config().vocab_size;
+    std::mt19937 rng(a.seed + a.batch);
+    const int total = 3 * a.batch;
+    int next_id = 0;
+    auto add = [&]() {
+        engine.scheduler.add_request(
+            make_request("s" + std::to_string(next_id++), random_prompt(rng, a.prompt_len, vocab), a.max_tokens));
+    };
+    auto run = [&](int count, long& tokens, int& steps) {
+        int added = 0;
+        for (; added < std::min(a.batch, count); added++) {
+            add();
+        }
+        while (engine.scheduler.has_requests()) {
+            for (const EngineCoreOutput& o : engine.step()) {
+                tokens += static_cast<long>(o.new_token_ids.size());
+                if (o.finish_reason != FinishReason::kRunning && added < count) {
+                    add();
+                    added++;
+                }
+            }
+            steps++;
+        }
+    };
+    long warm_tokens = 0;
+    int warm_steps = 0;
+    run(a.batch, warm_tokens, warm_steps);
+    long tokens = 0;
+    int steps = 0;
+    const auto t0 = Clock::now();
+    run(total, tokens, steps);
+    const double wall_ms = ms_since(t0);
+    std::printf(
+        "{\"output_tokens_per_s\": %.1f, \"total_tokens_per_s\": %.1f, \"requests\": %d, \"steps\": %d, "
+        "\"wall_s\": %.3f, \"in_flight\": %d, \"prompt_len\": %d, \"outputs\": %d}\n",
+        tokens * 1e3 / wall_ms, (tokens + static_cast<double>(total) * a.prompt_len) * 1e3 / wall_ms, total, steps,
+        wall_ms / 1e3, a.batch, a.prompt_len, a.max_tokens);
+    return 0;
+}
+
 int run_generate(const Args& a, const Config& config)
 {
     Engine engine(config);
@@ -335,6 +383,9 @@ int main(int argc, char** argv)
         config.enable_cuda_graph = a.cuda_graph;
         if (a.mode == "bench") {
             return run_bench(a, config);
+        }
+        if (a.mode == "serve") {
+            return run_serve(a, config);
         }
         if (a.mode == "generate") {
             return run_generate(a, config);

@@ -127,26 +127,31 @@ def make_engine(folder: str, batch: int, args):
     from cuinfer_b200.engine.core import EngineCore
 
     pages_per_request = (CONTEXT + BLOCK_SIZE - 1) // BLOCK_SIZE
-    config = EngineConfig(model_path=folder, block_size=BLOCK_SIZE, dtype="bfloat16",
-                          num_blocks=batch * pages_per_request + 8, max_num_seqs=max(batch, 8),
+    # --pool-from-memory: the cache pool is what 90 % of the device holds beside the weights, as in serving
+    pages = None if args.pool_from_memory else batch * pages_per_request + 8
+    config = EngineConfig(model_path=folder, block_size=BLOCK_SIZE, dtype="bfloat16", gpu_memory_utilization=0.9,
+                          num_blocks=pages, max_num_seqs=max(batch, 8),
                           max_num_scheduled_tokens=8192, enable_cuda_graph=not args.disable_cuda_graph, seed=0)
     return EngineCore(config)
 
 
-def measure_decode(folder: str, batch: int, steps: int, warmup: int, args, sample_clocks: bool = False) -> dict:
-    """Prefill ``batch`` requests so that decoding ends at CONTEXT tokens, then time ``steps`` decode steps."""
+def measure_decode(folder: str, batch: int, steps: int, warmup: int, args, sample_clocks: bool = False,
+                   context: int = 0) -> dict:
+    """Prefill ``batch`` requests so that decoding ends at ``context`` tokens (default: CONTEXT), then time ``steps``
+    decode steps."""
     import torch
 
     from cuinfer_b200 import SamplingParams, kernels
 
+    context = context or CONTEXT
     engine = make_engine(folder, batch, args)
     total_steps = warmup + steps
     # prompts are admitted a few per step under the token budget, so early requests decode while later ones
     # are still being prefilled: leave room for those extra tokens below the context limit
-    prefill_steps = (batch * CONTEXT + 8191) // 8192 + 2
-    prompt_len = CONTEXT - total_steps - prefill_steps - 1
+    prefill_steps = (batch * context + 8191) // 8192 + 2
+    prompt_len = context - total_steps - prefill_steps - 1
     gen = torch.Generator().manual_seed(1234 + batch)
-    params = SamplingParams(temperature=0.0, max_tokens=CONTEXT - prompt_len, ignore_eos=True)
+    params = SamplingParams(temperature=0.0, max_tokens=context - prompt_len, ignore_eos=True)
     for i in range(batch):
         prompt = torch.randint(0, MODEL["vocab_size"], (prompt_len,), generator=gen).tolist()
         engine.add_request(f"b{i}", prompt, params)
@@ -192,6 +197,56 @@ def measure_decode(folder: str, batch: int, steps: int, warmup: int, args, sampl
     }
     while engine.has_requests():
         engine.abort(list(engine.scheduler.requests))
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_generate(folder: str, in_flight: int, args, prompt_len: int = 1024, outputs: int = 128) -> dict:
+    """The reference's own workload (benchmark.sh:67-97: random prompts of 1 024 tokens, 128 outputs, a fixed number of
+    requests in flight) through ``LLM.generate``-style continuous batching: ``3 * in_flight`` requests are fed so that
+    ``in_flight`` are live at any time (a new one is added when one ends), host token ids in and out.  Every step is
+    a new mix of prompt portions and decoded tokens, so this is where the host's share of a step shows."""
+    import torch
+
+    from cuinfer_b200 import SamplingParams
+    from cuinfer_b200.config import EngineConfig
+    from cuinfer_b200.engine.core import EngineCore
+
+    pages = in_flight * ((prompt_len + outputs + BLOCK_SIZE) // BLOCK_SIZE + 1) + 8
+    engine = EngineCore(EngineConfig(model_path=folder, block_size=BLOCK_SIZE, dtype="bfloat16", num_blocks=pages,
+                                     max_num_seqs=max(in_flight, 8), max_num_scheduled_tokens=8192,
+                                     enable_cuda_graph=not args.disable_cuda_graph, seed=0))
+    gen = torch.Generator().manual_seed(4321 + in_flight)
+    total = 3 * in_flight
+    prompts = [torch.randint(0, MODEL["vocab_size"], (prompt_len,), generator=gen).tolist() for _ in range(total)]
+    params = SamplingParams(temperature=0.0, max_tokens=outputs, ignore_eos=True)
+
+    def run(first: int, count: int) -> tuple[int, float]:
+        nxt, done, tokens = first, 0, 0
+        for _ in range(min(in_flight, count)):
+            engine.add_request(f"g{nxt}", prompts[nxt % total], params)
+            nxt += 1
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while engine.has_requests():
+            for o in engine.step():
+                tokens += len(o.new_token_ids)
+                if o.finish_reason.value != "running":
+                    done += 1
+                    if nxt < first + count:
+                        engine.add_request(f"g{nxt}", prompts[nxt % total], params)
+                        nxt += 1
+        torch.cuda.synchronize()
+        return tokens, time.perf_counter() - t0
+
+    run(0, in_flight)                                   # warm-up: graphs captured, kernels loaded
+    steps0, graph0, replay0 = engine.runner.steps_run, engine.runner.graph_steps, engine.runner.step_graph_replays
+    tokens, wall = run(in_flight, total)
+    steps = engine.runner.steps_run - steps0
+    graphs = (engine.runner.graph_steps - graph0) + (engine.runner.step_graph_replays - replay0)
+    out = {"output_tokens_per_s": round(tokens / wall, 1), "total_tokens_per_s": round((tokens + total * prompt_len) / wall, 1),
+           "requests": total, "steps": steps, "steps_from_graphs": graphs, "wall_s": round(wall, 3)}
     del engine
     torch.cuda.empty_cache()
     return out
@@ -295,8 +350,8 @@ def reference_arm(args) -> int:
     cfg = dict(MODEL, max_position_embeddings=CONTEXT)
     tmp = tempfile.mkdtemp(prefix="cuinfer_reference_bench_")
 
-    def run(batch: int, steps: int, prefill_tokens: int) -> dict:
-        cmd = [binary, "--mode", "bench", "--model", tmp, "--batch", str(batch), "--context", str(CONTEXT),
+    def run(batch: int, steps: int, prefill_tokens: int, mode: str = "bench") -> dict:
+        cmd = [binary, "--mode", mode, "--prompt-len", "1024", "--max-tokens", "128", "--model", tmp, "--batch", str(batch), "--context", str(CONTEXT),
                "--steps", str(steps), "--warmup", str(args.warmup), "--prefill-tokens", str(prefill_tokens),
                "--block-size", str(BLOCK_SIZE), "--max-num-scheduled-tokens", "8192", "--max-num-seqs", "256",
                "--gpu-memory-utilization", "0.9", "--seed", "1234"]
@@ -318,6 +373,7 @@ def reference_arm(args) -> int:
             for b in (1, 64):
                 r = run(b, min(args.steps, 128), 0)
                 points[f"decode_b{b}"] = round(b * 1e3 / r["device_ms_per_step"], 1)
+        mixed = {f"in_flight_{c}": run(c, 1, 0, mode="serve") for c in (8, 32)} if args.mixed else None
     except Exception as exc:      # noqa: BLE001
         return unavailable(f"the reference engine did not run: {exc}")
     finally:
@@ -351,6 +407,8 @@ def reference_arm(args) -> int:
                                          / (main_run["prefill_ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
     if points:
         line["points"] = points
+    if mixed:
+        line["mixed"] = mixed
     print(json.dumps(line))
     return 0
 
@@ -370,6 +428,11 @@ def main() -> int:
                         help="tokens a request holds when decoding ends (default: the baseline's context length)")
     parser.add_argument("--disable-cuda-graph", action="store_true")
     parser.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the prefill measurement")
+    parser.add_argument("--pool-from-memory", action="store_true",
+                        help="size the cache pool from the device's free memory (90 %%) instead of what the batch needs")
+    parser.add_argument("--mixed", action="store_true",
+                        help="also run the reference's serving workload (1 024-token prompts, 128 outputs, 8 and 32 requests "
+                             "in flight) through the engine's continuous batching")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -394,13 +457,20 @@ def main() -> int:
     cfg = dict(MODEL, num_hidden_layers=args.layers)
     tmp = tempfile.mkdtemp(prefix="cuinfer_b200_bench_")
     try:
-        write_random_model(tmp, cfg, seed=0, std=0.02, dtype="bfloat16")
+        # a recipe, not tensors: the engine draws the weights on the device while it loads (seed 0, N(0, 0.02), gains 1)
+        write_random_model(tmp, cfg, seed=0, std=0.02, dtype="bfloat16", generator="counter", materialize=False)
         main_run = measure_decode(tmp, args.batch, args.steps, args.warmup, args, sample_clocks=True)
-        points, prefill = {}, None
+        points, prefill, mixed = {}, None, None
         if not args.skip_points:
             for b in (1, 64):
                 r = measure_decode(tmp, b, min(args.steps, 128), args.warmup, args)
                 points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+            for ctx in (2048, 3072):
+                if ctx < CONTEXT:
+                    r = measure_decode(tmp, args.batch, min(args.steps, 128), args.warmup, args, context=ctx)
+                    points[f"decode_b{args.batch}_ctx{ctx}"] = round(r["tokens_per_s"], 1)
+            if args.mixed:
+                mixed = {f"in_flight_{c}": measure_generate(tmp, c, args) for c in (8, 32)}
             p = measure_prefill(tmp, args)
             flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
             prefill = {"value": round(PREFILL_TOKENS / (p["ms"] / 1e3), 1), "tokens": PREFILL_TOKENS,
@@ -437,6 +507,8 @@ def main() -> int:
         line["prefill"] = prefill
     if points:
         line["points"] = points
+    if mixed:
+        line["mixed"] = mixed
     print(json.dumps(line))
     return 0
 

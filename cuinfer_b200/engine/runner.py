@@ -25,7 +25,7 @@ import torch
 from ..cache import CacheManager, CacheStorage, group_runs, page_bytes
 from ..config import EngineConfig, load_model_config
 from ..parts import DecoderModel, GroupView, PagedKV, StepContext
-from ..weights import WeightStore
+from ..weights import open_weight_store
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -80,7 +80,7 @@ class ModelRunner:
         self.architecture, self.model_config = load_model_config(model_dir)
         self.spec = self.architecture.spec(self.model_config)
         self.model = DecoderModel(self.spec, self.dtype)
-        store = WeightStore(model_dir, self.dtype, self.device)
+        store = open_weight_store(model_dir, self.dtype, self.device)
         try:
             self.model.load(store)
         finally:

@@ -80,6 +80,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_sample": [_P, _I, _I, _I, _P, _P, _P],
         "cib_argmax_rows": [_P, _I, _I, _I, _P, _P],
         "cib_selftest_bounded_wait": [ctypes.c_longlong, _P, _P, _P],
+        "cib_fill_random": [_P, _I, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _F, _I, _P],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -602,6 +603,17 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, silu_pair:
         1 if silu_pair else 0, M, N, K, _error_flag(a.device).data_ptr(), _stream())
     _check(rc, "gemm_tcgen05")
     note_flagged_launch()
+    _count()
+
+
+# ---- random weights ------------------------------------------------------------------------------------
+
+def fill_random(out: torch.Tensor, key: int, mean: float, std: float, factor: float = 1.0, via_bf16: bool = False) -> None:
+    """out.flat[i] = factor * (mean + std * z(key, i)), z approximately standard normal and a function of (key, i)
+    alone (``cuinfer_b200.weights.random_init.counter_normal`` computes the same values on the host)."""
+    rc = library().cib_fill_random(_cuda(out, "out"), _code(out, "out"), out.numel(), int(key) & 0xFFFFFFFFFFFFFFFF,
+                                   float(mean), float(std), float(factor), 1 if via_bf16 else 0, _stream())
+    _check(rc, "fill_random")
     _count()
 
 

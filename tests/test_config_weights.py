@@ -226,3 +226,26 @@ def test_sharded_checkpoint(tmp_path):
         json.dump(index, fh)
     with pytest.raises(WeightError, match="ghost"):
         Checkpoint(folder)
+
+
+def test_counter_generator_is_a_function_of_seed_name_and_index(tmp_path):
+    """The generator behind device-side random weights, on the host: element i depends on (seed, name, i) only —
+    a prefix of a longer draw is the shorter draw, another name or seed gives other values — the moments are those
+    of a normal, and a folder without tensors names its recipe instead."""
+    from cuinfer_b200.weights import counter_normal, random_tensors
+    from cuinfer_b200.weights.random_init import RANDOM_MARKER
+
+    a = counter_normal(77, 5000, 0.0, 1.0)
+    assert torch.equal(a[:1234], counter_normal(77, 1234, 0.0, 1.0))
+    assert not torch.equal(a, counter_normal(78, 5000, 0.0, 1.0))
+    big = counter_normal(5, 400000, 0.0, 1.0)
+    assert abs(float(big.mean())) < 0.01 and abs(float(big.std()) - 1.0) < 0.01 and 4.0 < float(big.abs().max()) <= 6.0
+    assert torch.equal(counter_normal(5, 100, 1.0, 0.1, 2.0), ((1.0 + 0.1 * counter_normal(5, 100, 0.0, 1.0).double()).float() * 2.0))
+    t1 = random_tensors(TINY_A, 3, generator="counter", gain_std=0.1, gains={"q_norm": 2.0})
+    t2 = random_tensors(TINY_A, 3, generator="counter", gain_std=0.1, gains={"q_norm": 2.0})
+    assert all(torch.equal(t1[k], t2[k]) for k in t1)
+    assert abs(float(t1["model.layers.0.self_attn.q_norm.weight"].mean()) - 2.0) < 0.2
+    folder = write_random_model(str(tmp_path / "m"), TINY_A, 3, generator="counter", materialize=False, dtype="bfloat16")
+    assert sorted(os.listdir(folder)) == ["config.json", RANDOM_MARKER]
+    with pytest.raises(ValueError, match="generator='counter'"):
+        write_random_model(str(tmp_path / "n"), TINY_A, 3, materialize=False)

@@ -374,3 +374,33 @@ def test_request_id_that_comes_back_gets_its_own_pages(model_folders, live):
             assert got[rid] == plain_qwen3.greedy_generate(pcfg, weights, prompts[rid], 24), (round_no, rid)
     assert engine.runner.graph_steps > 40
     engine.runner.manager.check()
+
+
+@pytest.mark.parametrize("stored, engine", [("float32", "float32"), ("bfloat16", "bfloat16"), ("float32", "bfloat16")])
+def test_weights_drawn_on_the_device_equal_the_host_generator(tmp_path, stored, engine):
+    """A folder that names a recipe instead of holding tensors: the engine fills its weights on the device, bit for
+    bit the values the host generator writes into a file (same seed, same names), under the same precision rule
+    (a gain stored in 32 bits stays so on a bfloat16 engine); and generation from both folders gives the same tokens."""
+    from conftest import TINY_B
+    from cuinfer_b200 import LLM, SamplingParams
+    from cuinfer_b200.weights import write_random_model
+
+    kw = dict(std=0.05, gain_std=0.1, dtype=stored, gains={"q_norm": 2.0}, generator="counter")
+    on_disk = write_random_model(str(tmp_path / "disk"), TINY_B, 9, **kw)
+    recipe = write_random_model(str(tmp_path / "recipe"), TINY_B, 9, materialize=False, **kw)
+    a = LLM(on_disk, dtype=engine, block_size=16, num_blocks=32, max_num_seqs=4)
+    b = LLM(recipe, dtype=engine, block_size=16, num_blocks=32, max_num_seqs=4)
+    ma, mb = a.engine.runner.model, b.engine.runner.model
+    pairs = [(ma.embedding, mb.embedding), (ma.lm_head.weight, mb.lm_head.weight), (ma.final_norm.weight, mb.final_norm.weight)]
+    for x, y in zip(ma.blocks, mb.blocks):
+        pairs += [(x.mixer.qkv.weight, y.mixer.qkv.weight), (x.mixer.o.weight, y.mixer.o.weight),
+                  (x.mixer.q_norm_weight, y.mixer.q_norm_weight), (x.mixer.k_norm_weight, y.mixer.k_norm_weight),
+                  (x.feed_forward.gate_up.weight, y.feed_forward.gate_up.weight), (x.feed_forward.down.weight, y.feed_forward.down.weight),
+                  (x.mixer_norm.weight, y.mixer_norm.weight), (x.feed_forward_norm.weight, y.feed_forward_norm.weight)]
+    for x, y in pairs:
+        assert x.dtype == y.dtype and x.shape == y.shape and torch.equal(x.cpu(), y.cpu())
+    if stored == "float32" and engine == "bfloat16":
+        assert ma.final_norm.weight.dtype == torch.float32 and ma.embedding.dtype == torch.bfloat16
+    prompts = [random_tokens(TINY_B["vocab_size"], n, 950 + i) for i, n in enumerate([11, 40])]
+    p = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    assert [r.token_ids for r in a.generate(prompts, p)] == [r.token_ids for r in b.generate(prompts, p)]
