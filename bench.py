@@ -240,7 +240,8 @@ def measure_generate(folder: str, in_flight: int, args, prompt_len: int = 1024, 
         torch.cuda.synchronize()
         return tokens, time.perf_counter() - t0
 
-    run(0, in_flight)                                   # warm-up: graphs captured, kernels loaded
+    run(0, in_flight)                                   # warm-up, twice: kernels loaded, then the step shapes that come
+    run(0, in_flight)                                   # back are captured as graphs (a server does this once)
     steps0, graph0, replay0 = engine.runner.steps_run, engine.runner.graph_steps, engine.runner.step_graph_replays
     tokens, wall = run(in_flight, total)
     steps = engine.runner.steps_run - steps0
