@@ -3,9 +3,12 @@
 Whole sequences, no cache, no batching, one function per part, written from the reference's formulas
 (every function cites the file and lines it restates).  It shares no code with ``cuinfer_b200``: it reads
 ``config.json`` and ``model.safetensors`` by itself (through the ``safetensors`` package) and computes with
-torch on the CPU.  The reference's own model code cannot run here: every op exists only as a CUDA kernel
+torch on the CPU.  The reference's own model code cannot run on a CPU: every op exists only as a CUDA kernel
 with fixed sizes (hidden 1024/2048, head_dim 128; csrc/ops/embedding.cu:74-88, csrc/ops/qk_norm_rope_fused.cu:278)
-and the model constructor copies to a GPU (csrc/model/causal_lm.cpp:24-33), so this file rests on the formulas.
+and the model constructor copies to a GPU (csrc/model/causal_lm.cpp:24-33), so this file is written from the formulas.
+It is anchored on the reference all the same: ``tests/golden/reference_tokens.json`` holds greedy tokens that the
+unmodified reference engine generated on a B200 for a small random model (``tests/golden/make_reference_tokens.py``
+made it), and ``tests/test_plain.py`` checks this implementation against them.
 
 Intermediate roundings that the reference's bfloat16 kernels make (after the norm product, between q/k norm
 and RoPE, of the softmax weights before they multiply V) are left out on purpose: this is the exact

@@ -83,3 +83,30 @@ def test_plain_sampler():
     p = torch.softmax(logits, 0)
     for i in range(5):
         assert abs(draws.count(i) / 1000 - float(p[i])) < 0.01
+
+
+def test_plain_agrees_with_the_reference_engine_golden_tokens(tmp_path):
+    """tests/golden/reference_tokens.json holds greedy tokens that the UNMODIFIED reference engine generated on a
+    B200 for a small random model (three layers of the Qwen3-0.6B widths, vocabulary 2 048; the script beside the file
+    made it).  The same weights are rebuilt here (counter-based generator: the same bits on every machine) and the plain
+    implementation is run over prompt + tokens: every token of the reference must be the plain implementation's best
+    token at its place, or, where bfloat16 rounding can turn a near-tie, within a small margin of the best."""
+    import json
+    import os
+
+    from cuinfer_b200.weights import write_random_model
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_tokens.json")
+    golden = json.load(open(path))
+    folder = write_random_model(str(tmp_path / "m"), golden["config"], **golden["weights"])
+    cfg, weights = P.load_folder(folder)
+    exact = total = 0
+    for prompt, tokens in zip(golden["prompts"], golden["tokens"]):
+        ids = list(prompt) + list(tokens)
+        logits = P.forward(cfg, weights, ids[:-1])
+        for j, tok in enumerate(tokens):
+            row = logits[len(prompt) - 1 + j]
+            total += 1
+            exact += int(torch.argmax(row)) == tok
+            assert float(row.max() - row[tok]) <= 0.03 * float(row.abs().max()), (len(prompt), j, tok, int(torch.argmax(row)))
+    assert exact >= 0.9 * total, f"only {exact} of {total} tokens are the plain implementation's best"
