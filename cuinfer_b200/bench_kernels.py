@@ -124,6 +124,8 @@ def gemm(args) -> dict:
             kernels.gemm_tcgen05(x, w[i % copies], out)
         elif args.impl == "wstream":
             kernels.gemm_wstream(x, w[i % copies], out)
+        elif args.impl == "skinny":
+            kernels.gemm_skinny(w[i % copies], out, act=x)
         elif args.impl == "cublas":
             torch.mm(x, w[i % copies].t(), out=out)
         else:
@@ -200,7 +202,7 @@ def main(argv=None) -> int:
     g.add_argument("--n", type=int, default=4096)
     g.add_argument("--k", type=int, default=1024)
     g.add_argument("--f32-out", action="store_true")
-    g.add_argument("--impl", default="auto", choices=["auto", "tcgen05", "wstream", "cublas"])
+    g.add_argument("--impl", default="auto", choices=["auto", "tcgen05", "wstream", "skinny", "cublas"])
     g.add_argument("--pdl", action="store_true", help="launch with programmatic dependent launch")
     g.add_argument("--copies", type=int, default=8)
     g.add_argument("--iters", type=int, default=20)

@@ -107,7 +107,10 @@ class Linear:
             return None
         out_cols = N // 2 if silu_pair else N
         from . import gemm_dispatch
-        if K > gemm_dispatch.FEW_ROWS_LONG_K:
+        choice = gemm_dispatch.few_rows_kernel(M, N, K)
+        if choice == "library":
+            return None           # the library product (and the activation kernel after it) in forward()
+        if choice == "wstream":
             # long K: the weight-streaming kernel (no norm prologue; the gate is in its epilogue)
             rows = x.materialize() if lazy else x
             if (not silu_pair or rows.dtype != torch.bfloat16 or rows.stride(1) != 1 or rows.stride(0) % 8 or w.stride(0) % 8
