@@ -97,11 +97,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
     __shared__ float s_m[2][128];          // [group][row]: the group's reference maximum at the end
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = blockIdx.y;
+    const int kvh = blockIdx.x;     // heads vary fastest: every head's longest tile starts before any shorter one
     const int g = nq / nkv;
 
     if (tid == 0) {
-        int t = gridDim.x - 1 - blockIdx.x, r = 0;      // later (longer) tiles first
+        int t = gridDim.y - 1 - blockIdx.y, r = 0;      // later (longer) tiles first
         for (; r < num_requests; ++r) {
             const int tiles = ((query_start_loc[r + 1] - query_start_loc[r]) * g + kM - 1) / kM;
             if (t < tiles) break;
@@ -445,7 +445,7 @@ extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int
     CIB_REQUIRE(cib_attention_tcgen05_supports(head_dim, nq, nkv, page_size),
                 "attention_tcgen05: head_dim %d, %d/%d heads, page size %d are not taken (head size 128, heads per kv head dividing 128, pages of 8, 16, 32, ... slots)",
                 head_dim, nq, nkv, page_size);
-    CIB_REQUIRE(num_requests >= 0 && num_tiles >= 0 && nkv <= 65535 && num_pages > 0 && table_stride > 0, "attention_tcgen05: bad sizes");
+    CIB_REQUIRE(num_requests >= 0 && num_tiles >= 0 && num_tiles <= 65535 && num_pages > 0 && table_stride > 0, "attention_tcgen05: bad sizes");
     CIB_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && out_stride % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)cache % 16) == 0,
                 "attention_tcgen05: rows must be 16-byte aligned");
     CIB_REQUIRE(error_flag != nullptr, "attention_tcgen05: error flag missing");
@@ -466,7 +466,7 @@ extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int
         }
         configured = true;
     }
-    dim3 grid(num_tiles, nkv);
+    dim3 grid(nkv, num_tiles);
     fa::attention_tcgen05_kernel<<<grid, fa::kThreads, fa::kSmemBytes, stream>>>(
         kv_map, num_pages, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, page_size, block_table, table_stride,
         query_start_loc, seq_lens, num_requests, nq, nkv, scale * 1.4426950408889634f, window, error_flag);
