@@ -3,9 +3,8 @@
 Names, defaults and range checks follow the reference's ``Config`` (csrc/engine/config.h:9-28)
 and its Python mirror (cuinfer/engine.py:19-34).  Added here: ``dtype`` (the reference is
 bfloat16 only), ``num_blocks`` (an explicit page count instead of a share of free memory),
-``seed`` (the reference seeds its sampler from the OS, csrc/executor/sampler.cpp:12),
-``state_bytes`` (size of the per-request fixed state slot) and ``decode_run_ahead`` (launch the next decode step
-before the tokens of the one in flight have been read; see ``engine/core.py``).
+``seed`` (the reference seeds its sampler from the OS, csrc/executor/sampler.cpp:12) and ``decode_run_ahead``
+(launch the next decode step before the tokens of the one in flight have been read; see ``engine/core.py``).
 """
 from __future__ import annotations
 
