@@ -91,7 +91,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
     uint64_t* k_free = bars + 11;      // [kKBufs <= 3] S has read a key buffer (early: its next keys can be fetched)
     uint64_t* v_free = bars + 14;      // [2] P V has read a value buffer
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    __shared__ int s_req, s_tile, s_abort;
+    __shared__ int s_req, s_tile, s_abort, s_q0, s_n, s_seq;
     __shared__ float s_mx[2][2][2][128];   // [group][tile parity within the group][column half][row]: the halves' maxima
     __shared__ float s_l[2][2][128];       // [group][column half][row]: the halves' sums at the end
     __shared__ float s_m[2][128];          // [group][row]: the group's reference maximum at the end
@@ -108,6 +108,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             t -= tiles;
         }
         s_req = r; s_tile = t; s_abort = 0;
+        if (r < num_requests) {     // read here once, so that the other threads need no round trip of their own after the barrier
+            s_q0 = query_start_loc[r];
+            s_n = query_start_loc[r + 1] - query_start_loc[r];
+            s_seq = seq_lens[r];
+        }
         for (int i = 0; i < kKBufs; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_free[i], 1); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&v_full[i], 1); mbar_init(&v_free[i], 1); mbar_init(&s_full[i], 1);
@@ -132,9 +137,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
 
     int q0 = 0, n = 0, seq_len = 0, row0 = 0, rows_total = 0, num_tiles = 0, k_lo = 0;
     if (active) {
-        q0 = query_start_loc[r];
-        n = query_start_loc[r + 1] - q0;
-        seq_len = seq_lens[r];
+        q0 = s_q0;
+        n = s_n;
+        seq_len = s_seq;
         rows_total = n * g;
         row0 = s_tile * kM;
         const int last_row = min(row0 + kM, rows_total) - 1;
@@ -157,7 +162,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    __syncthreads();
+    // the MMA warp waits for the query tile; the producer warps do not, so that the first keys and values are on their
+    // way while the queries are still being copied
+    if (warp <= kMmaWarp) asm volatile("bar.sync 10, %0;" ::"r"((kMmaWarp + 1) * 32) : "memory");
 
     // tensor memory: S of group 0 | S of group 1 | O of group 0 | O of group 1, 128 columns each; P of a group (bfloat16,
     // two keys to a column) takes the first 64 columns of the group's S once the softmax holds S in registers
