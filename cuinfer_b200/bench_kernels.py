@@ -47,7 +47,7 @@ def attention_decode(args) -> dict:
     q = torch.randn(R, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16)
     out = torch.empty(R, nq * d, device=dev, dtype=torch.bfloat16)
     sl = torch.full((R,), ctx, dtype=torch.int32, device=dev)
-    splits = args.splits or kernels.decode_splits(R, nkv, ctx)
+    splits = args.splits or kernels.decode_splits(R, nkv, ctx, tma=kernels.decode_tma_takes(ps, d, 0))
     scale = 1.0 / math.sqrt(d)
 
     def run(i):

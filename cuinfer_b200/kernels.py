@@ -272,14 +272,33 @@ def paged_attention_decode_supports(head_dim: int, num_q_heads: int, num_kv_head
 decode_tma = os.environ.get("CUINFER_B200_DECODE_TMA", "1") != "0"
 
 
-def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots: int = 296) -> int:
-    """How many CTAs share the keys of one (request, kv head).
+DECODE_TMA_MIN_KEYS = 1024      # keys per CTA from which the TMA path of the decode kernel pays inside a step (measured)
+
+
+def decode_tma_takes(page_size: int, head_dim: int, window: int) -> bool:
+    """Whether the decode attention can stream its keys and values as TMA page boxes for this cache layout (else
+    cp.async only): whole 16-slot blocks inside a page, 64-column panels, no window."""
+    return decode_tma and page_size % 16 == 0 and head_dim % 64 == 0 and window <= 0
+
+
+def decode_uses_tma(max_seq_len: int, splits: int) -> bool:
+    """The TMA path streams faster, but it starts later after the kernel before it in a step (the cp.async path asks
+    for its first blocks before that kernel has ended): timed alone it wins at every size, inside a decode step only
+    for long streams per CTA (batch 1 with 26 CTAs of 160 keys per head: 919 tokens/s against 974 on cp.async)."""
+    return -(-max_seq_len // splits) >= DECODE_TMA_MIN_KEYS
+
+
+def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots: int = 296, tma: bool = False) -> int:
+    """How many CTAs share the keys of one (request, kv head).  ``tma``: the cache layout allows the TMA path, which
+    a split then takes if it leaves a CTA ``DECODE_TMA_MIN_KEYS`` keys or more.
 
     The GPU runs ``slots`` CTAs of this kernel at a time (two on each of the 148 SMs); a CTA's four warps take
-    16-key blocks in turn, so a CTA's share counts in steps of 64 keys.  A launch is estimated, in nanoseconds, as
-    the larger of the time the memory needs for all keys and values, and (rounds of CTAs) x (keys per CTA x 19.5
-    + 4400 for a CTA's start, merge and partial results), plus 75 per split for the combine.  The constants were
-    fitted to timings at batch 1, 8 and 64 with 4096 keys of head size 128.  The smallest estimate wins.
+    16-key blocks in turn, so a CTA's share counts in steps of 64 keys.  A launch is estimated, in nanoseconds, round
+    of CTAs by round: a round of n CTAs takes keys per CTA x (the larger of a CTA's own pace per key and n x 0.072, the
+    memory's pace when n CTAs stream at once) plus a fixed cost for a CTA's start and its partial results; splitting
+    adds 3000 for the combine and 160 per split.  A CTA's own pace is 16 per key and 3000 fixed on the TMA path, 18 and
+    4000 on the cp.async path.  The constants were fitted to timings at batch 1 to 128 with 300 to 9000 keys of head
+    size 128 (largest miss 1.7 us, 9 % r.m.s. error of the estimate).  The smallest estimate wins.
     """
     pairs = max(1, num_requests * num_kv_heads)
     best, best_cost = 1, None
@@ -287,16 +306,17 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots:
         keys = -(-(-(-max_seq_len // s)) // 64) * 64
         if s > 1 and (s - 1) * keys >= max_seq_len:
             continue                                   # the last CTA would get nothing: a smaller s does the same
-        ctas = pairs * s
-        memory = ctas * keys * 0.0788
-        chain = -(-ctas // slots) * (keys * 19.5 + 4400.0)
-        cost = max(memory, chain) + (75.0 * s if s > 1 else 0.0)
+        per_key, fixed = (16.0, 3000.0) if tma and decode_uses_tma(max_seq_len, s) else (18.0, 4000.0)
+        full, rest = divmod(pairs * s, slots)
+        cost = full * (keys * max(per_key, 0.072 * slots) + fixed)
+        if rest:
+            cost += keys * max(per_key, 0.072 * rest) + fixed
+        if s > 1:
+            cost += 3000.0 + 160.0 * s
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
 
-
-DECODE_TMA_MIN_KEYS = 1024      # keys per CTA from which the TMA path of the decode kernel pays (measured)
 
 # A kernel of the decode chain may ask for the weights of the kernel after it to be fetched into the L2 while it runs.
 # That pays where the chain is bound by latencies and the weights are small beside the 126 MB L2 (every matrix of the

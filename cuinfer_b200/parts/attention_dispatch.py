@@ -1,7 +1,8 @@
 """Choice of the paged-attention kernel for a step.
 
 float32 always runs the all-sizes kernel.  bfloat16: a step of single decoded tokens runs the split-KV kernel (its
-TMA path when a CTA streams at least ``kernels.DECODE_TMA_MIN_KEYS`` keys, else its cp.async path); any
+TMA path where the cache layout allows and a CTA streams at least ``kernels.DECODE_TMA_MIN_KEYS`` keys, else its
+cp.async path); any
 other step runs the tcgen05 kernel (head size 128, heads per kv head dividing 128) or the mma.sync kernel (head
 size 64 or 128); other head sizes fall back to the all-sizes kernel.  ``CUINFER_B200_ATTENTION=mma`` keeps prompt
 portions off the tcgen05 kernel (for comparisons).
@@ -26,9 +27,9 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: Step
     if (qkv.dtype == torch.bfloat16 and ctx.decode_only
             and kernels.paged_attention_decode_supports(head_dim, num_heads, num_kv_heads)):
         longest = max(1, ctx.max_seq_len)
-        splits = kernels.decode_splits(ctx.num_requests, num_kv_heads, longest)
-        # the TMA path of the kernel streams faster but takes longer to start: only for long streams per CTA
-        tma = -(-longest // splits) >= kernels.DECODE_TMA_MIN_KEYS
+        tma = kernels.decode_tma_takes(kv.group.page_size, head_dim, window)
+        splits = kernels.decode_splits(ctx.num_requests, num_kv_heads, longest, tma=tma)
+        tma = tma and kernels.decode_uses_tma(longest, splits)
         kernels.paged_attention_decode(qkv, out, kv.cache, kv.group.block_table, ctx.seq_lens, num_heads,
                                        num_kv_heads, head_dim, scale, window, splits, tma=tma, warm=warm)
         return
