@@ -16,15 +16,19 @@ def test_decode_splits_is_sane_for_every_shape():
         requests = rnd.choice([1, 2, 3, 5, 8, 12, 17, 32, 64, 200])
         kv_heads = rnd.choice([1, 2, 4, 8, 16])
         keys = rnd.choice([1, 15, 64, 65, 500, 1024, 4096, 5000, 32768, 131072])
-        s = kernels.decode_splits(requests, kv_heads, keys)
-        assert 1 <= s <= 64
-        if s > 1:
-            share = -(-(-(-keys // s)) // 64) * 64            # keys per CTA, in steps of 64
-            assert (s - 1) * share < keys                       # the last CTA still has keys to read
+        for tma in (False, True):                               # the cache layout allows the TMA path or not
+            s = kernels.decode_splits(requests, kv_heads, keys, tma=tma)
+            assert 1 <= s <= 64
+            if s > 1:
+                share = -(-(-(-keys // s)) // 64) * 64        # keys per CTA, in steps of 64
+                assert (s - 1) * share < keys                   # the last CTA still has keys to read
     # few (request, kv head) pairs and many keys: split; the GPU already full of pairs: do not
     assert kernels.decode_splits(1, 8, 4096) > 8 and kernels.decode_splits(8, 8, 4096) >= 2
     assert kernels.decode_splits(64, 8, 4096) == 1 and kernels.decode_splits(256, 8, 512) == 1
     assert kernels.decode_splits(1, 8, 16) == 1                 # one block of keys cannot be shared
+    # 24 requests x 8 heads leave a third of the GPU free, but a second round of CTAs would cost more than it brings
+    assert kernels.decode_splits(24, 8, 2048, tma=True) == 1 and kernels.decode_uses_tma(2048, 1)
+    assert not kernels.decode_uses_tma(4096, 32)                # short streams per CTA stay on cp.async
     # more keys never mean fewer CTAs for the same batch
     for requests in (1, 2, 8):
         counts = [kernels.decode_splits(requests, 8, n) for n in (256, 1024, 4096, 16384)]
