@@ -380,40 +380,54 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // weights of the splits first (one parallel round of loads), then the weighted sums with several
-    // loads in flight per thread
+    // maxima and sums of all splits in one parallel round of loads; a warp per row turns them into weights (lanes over
+    // the splits); then the weighted sums with up to sixteen loads in flight per thread.  (Read one by one in a loop
+    // over the splits, the sums cost a round trip to the L2 each: some 5 us with 32 splits.)
     const size_t base = ((size_t)r * nkv + kvh) * splits;
-    float* sm_w = reinterpret_cast<float*>(smem_raw);            // [g][splits] weight of each split
-    float* sm_inv = sm_w + (size_t)g * splits;                    // [g] 1 / total
+    float* sm_w = reinterpret_cast<float*>(smem_raw);            // [g][splits] maximum, then weight of each split
+    float* sm_ls = sm_w + (size_t)g * splits;                     // [g][splits] sum of each split
+    float* sm_inv = sm_ls + (size_t)g * splits;                   // [g] 1 / total
     for (int idx = threadIdx.x; idx < g * splits; idx += blockDim.x) {
         const int row = idx / splits, sp = idx - row * splits;
-        sm_w[idx] = __ldcg(&part_ml[((base + sp) * g + row) * 2]);
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(&part_ml[((base + sp) * g + row) * 2]));
+        sm_w[idx] = ml.x;
+        sm_ls[idx] = ml.y;
     }
     __syncthreads();
-    if (threadIdx.x < g) {
-        const int row = threadIdx.x;
+    for (int row = warp; row < g; row += kDecWarps) {
         float M = -INFINITY;
-        for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, sm_w[row * splits + sp]);
+        for (int sp = lane; sp < splits; sp += 32) M = fmaxf(M, sm_w[row * splits + sp]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
         float L = 0.f;
-        for (int sp = 0; sp < splits; ++sp) {
+        for (int sp = lane; sp < splits; sp += 32) {
             const float ms = sm_w[row * splits + sp];
             const float f = (ms == -INFINITY || M == -INFINITY) ? 0.f : exp2f(ms - M);
             sm_w[row * splits + sp] = f;
-            L += __ldcg(&part_ml[((base + sp) * g + row) * 2 + 1]) * f;
+            L += sm_ls[row * splits + sp] * f;
         }
-        sm_inv[row] = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+        if (lane == 0) sm_inv[row] = L > 0.f ? 1.f / L : 0.f;
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
         const int row = idx / D, dim = idx - row * D;
         float O = 0.f;
         int sp = 0;
-        for (; sp + 8 <= splits; sp += 8) {
-            float v[8];
+        for (; sp + 16 <= splits; sp += 16) {
+            float v[16];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __ldcg(&part_o[((base + sp + u) * g + row) * D + dim]);
+            for (int u = 0; u < 16; ++u) v[u] = __ldcg(&part_o[((base + sp + u) * g + row) * D + dim]);
 #pragma unroll
-            for (int u = 0; u < 8; ++u) O = fmaf(v[u], sm_w[row * splits + sp + u], O);
+            for (int u = 0; u < 16; ++u) O = fmaf(v[u], sm_w[row * splits + sp + u], O);
+        }
+        for (; sp + 4 <= splits; sp += 4) {
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = __ldcg(&part_o[((base + sp + u) * g + row) * D + dim]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) O = fmaf(v[u], sm_w[row * splits + sp + u], O);
         }
         for (; sp < splits; ++sp) O = fmaf(__ldcg(&part_o[((base + sp) * g + row) * D + dim]), sm_w[row * splits + sp], O);
         out[(size_t)r * out_stride + (size_t)(kvh * g + row) * D + dim] = __float2bfloat16_rn(O * sm_inv[row]);
@@ -440,7 +454,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
         return -1;
     size_t smem = DecodeSmem<D>::kTotal + (tma ? 1024 : 0);
     size_t merge = (size_t)(2 * kDecWarps * 16 + kDecWarps * g * D) * sizeof(float) + (tma ? 1024 : 0);
-    const size_t combine = (size_t)(g * splits + g) * sizeof(float) + (tma ? 1024 : 0);
+    const size_t combine = (size_t)(2 * g * splits + g) * sizeof(float) + (tma ? 1024 : 0);
     if (combine > merge) merge = combine;
     if (merge > smem) smem = merge;
     // the larger shared-memory limit is a property of the kernel on one device: set once per device
@@ -512,6 +526,7 @@ extern "C" int cib_paged_attention_decode(const void* q, int q_stride, void* out
     CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0, "paged_attention_decode: bad cache geometry");
     CIB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4) == 0, "paged_attention_decode: q rows must be 4-byte aligned");
     CIB_REQUIRE(splits == 1 || (scratch && counters), "paged_attention_decode: splits need scratch and counters");
+    CIB_REQUIRE(((uintptr_t)scratch % 8) == 0, "paged_attention_decode: the scratch must be 8-byte aligned");
     CIB_REQUIRE(num_requests <= 65535 && nkv <= 65535, "paged_attention_decode: grid too large");
     if (num_requests == 0) return 0;
     float* part_o = scratch;

@@ -296,7 +296,7 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots:
     16-key blocks in turn, so a CTA's share counts in steps of 64 keys.  A launch is estimated, in nanoseconds, round
     of CTAs by round: a round of n CTAs takes keys per CTA x (the larger of a CTA's own pace per key and n x 0.072, the
     memory's pace when n CTAs stream at once) plus a fixed cost for a CTA's start and its partial results; splitting
-    adds 3000 for the combine and 160 per split.  A CTA's own pace is 16 per key and 3000 fixed on the TMA path, 18 and
+    adds 3000 for the combine and 40 per split.  A CTA's own pace is 16 per key and 3000 fixed on the TMA path, 18 and
     4000 on the cp.async path.  The constants were fitted to timings at batch 1 to 128 with 300 to 9000 keys of head
     size 128 (largest miss 1.7 us, 9 % r.m.s. error of the estimate).  The smallest estimate wins.
     """
@@ -312,7 +312,7 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots:
         if rest:
             cost += keys * max(per_key, 0.072 * rest) + fixed
         if s > 1:
-            cost += 3000.0 + 160.0 * s
+            cost += 3000.0 + 40.0 * s
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
