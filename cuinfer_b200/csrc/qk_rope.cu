@@ -99,7 +99,6 @@ __global__ void qk_norm_rope_kv_write_fast_kernel(T* __restrict__ qkv, int row_s
                                                   int page_size, int nq, int nkv, int write_cache) {
     constexpr int D = E * 32;
     griddep_launch();
-    griddep_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int head = blockIdx.y * kRopeWarps + warp;
@@ -109,6 +108,8 @@ __global__ void qk_norm_rope_kv_write_fast_kernel(T* __restrict__ qkv, int row_s
     const bool is_q = head < nq;
     const bool is_k = !is_q && head < nq + nkv;
     const int kvh = is_q ? 0 : (is_k ? head - nq : head - nq - nkv);
+    // What does not come from the kernel before this one (the slot, the position and its table row, the gains) is
+    // fetched before `griddepcontrol.wait`: after it only the head's own values are a round trip away.
     T* dst = src;
     if (!is_q) {
         const int slot = slot_mapping[t];
@@ -118,19 +119,14 @@ __global__ void qk_norm_rope_kv_write_fast_kernel(T* __restrict__ qkv, int row_s
         dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * D + lane * E;
     }
     using Vec = LaneValues<T, E>;
-    const Vec rawv = *reinterpret_cast<const Vec*>(src);
-    const T* raw = rawv.v;
-    if (!is_q && !is_k) {
-        *reinterpret_cast<Vec*>(dst) = rawv;
-        return;
-    }
     float x[E], wv[E], cs[2 * E];
+    const bool is_v = !is_q && !is_k;
     const AnyVec& w = is_q ? q_weight : k_weight;
-    if (has_norm) {
+    if (has_norm && !is_v) {
 #pragma unroll
         for (int e = 0; e < E; ++e) wv[e] = w[lane * E + e];
     }
-    if (has_rope) {
+    if (has_rope && !is_v) {
         int pos = positions[t];
         pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
         const float* tp = rope_table + (size_t)pos * D + 2 * ((lane & 15) * E);
@@ -144,6 +140,13 @@ __global__ void qk_norm_rope_kv_write_fast_kernel(T* __restrict__ qkv, int row_s
             const float2 v = *reinterpret_cast<const float2*>(tp);
             cs[0] = v.x, cs[1] = v.y;
         }
+    }
+    griddep_wait();
+    const Vec rawv = *reinterpret_cast<const Vec*>(src);
+    const T* raw = rawv.v;
+    if (is_v) {
+        *reinterpret_cast<Vec*>(dst) = rawv;
+        return;
     }
 #pragma unroll
     for (int e = 0; e < E; ++e) x[e] = to_f32(raw[e]);
