@@ -30,7 +30,6 @@ namespace cib {
 constexpr int kDecWarps = 4;
 constexpr int kDecStages = 3;
 constexpr int kDecKeys = 16;   // keys per warp block
-constexpr int kMaxDevices = 64;  // per-device set-up (shared-memory limit, address of the built-in scratch) is kept for this many
 
 template <int D>
 struct DecodeSmem {
@@ -457,27 +456,10 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     const size_t combine = (size_t)(2 * g * splits + g) * sizeof(float) + (tma ? 1024 : 0);
     if (combine > merge) merge = combine;
     if (merge > smem) smem = merge;
-    // the larger shared-memory limit is a property of the kernel on one device: set once per device
     {
-        static std::mutex mutex;
-        static bool configured[kMaxDevices] = {false};
-        int dev = -1;
-        cudaError_t e = cudaGetDevice(&dev);
-        if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
-            set_error("paged_attention_decode: cannot tell the current device (%s)", cudaGetErrorString(e));
-            return -2;
-        }
-        std::lock_guard<std::mutex> lock(mutex);
-        if (!configured[dev]) {
-            e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
-            if (e == cudaSuccess)
-                e = cudaFuncSetAttribute(paged_attention_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
-            if (e != cudaSuccess) {
-                set_error("paged_attention_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
-                return -2;
-            }
-            configured[dev] = true;
-        }
+        static SmemLimit limit_async, limit_tma;
+        if (int rc = raise_smem_limit(limit_async, paged_attention_decode_kernel<D, false>, 225 * 1024, "paged_attention_decode")) return rc;
+        if (int rc = raise_smem_limit(limit_tma, paged_attention_decode_kernel<D, true>, 225 * 1024, "paged_attention_decode")) return rc;
     }
     CIB_REQUIRE(smem <= 225 * 1024, "paged_attention_decode: needs %zu bytes of shared memory", smem);
     dim3 grid(splits, nkv, num_requests);

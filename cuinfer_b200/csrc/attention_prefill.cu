@@ -272,15 +272,8 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
                           const int* seq_lens, int num_requests, int num_tiles, int nq, int nkv, float scale, int window,
                           int pair, cudaStream_t stream) {
     const size_t smem = (size_t)(kPfStages * 2 * kPfN * D) * sizeof(__nv_bfloat16);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) {
-            set_error("paged_attention_prefill: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
-            return -2;
-        }
-        configured = true;
-    }
+    static SmemLimit limit;
+    if (int rc = raise_smem_limit(limit, paged_attention_prefill_kernel<D>, smem, "paged_attention_prefill")) return rc;
     dim3 grid(num_tiles, nkv);
     paged_attention_prefill_kernel<D><<<grid, kPfWarps * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache, num_pages,

@@ -464,15 +464,8 @@ extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int
     if (encode_tensor_map_bf16_2d(&kv_map, cache, (unsigned long long)total_rows, fa::kD, fa::kD, 64,
                                   page_size < fa::kN ? page_size : fa::kN, "attention_tcgen05") != 0)
         return -1;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(fa::attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::kSmemBytes);
-        if (e != cudaSuccess) {
-            set_error("attention_tcgen05: cannot raise shared memory to %d: %s", fa::kSmemBytes, cudaGetErrorString(e));
-            return -2;
-        }
-        configured = true;
-    }
+    static SmemLimit limit;
+    if (int rc = raise_smem_limit(limit, fa::attention_tcgen05_kernel, fa::kSmemBytes, "attention_tcgen05")) return rc;
     dim3 grid(nkv, num_tiles);
     fa::attention_tcgen05_kernel<<<grid, fa::kThreads, fa::kSmemBytes, stream>>>(
         kv_map, num_pages, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, page_size, block_table, table_stride,

@@ -11,6 +11,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 namespace cib {
 
 enum DType : int { kF32 = 0, kBF16 = 1 };
@@ -25,6 +27,33 @@ void set_error(const char* fmt, ...);
 // issue TMA copies include the driver header).  0, or -1 with the error text set.
 int encode_tensor_map_bf16_2d(void* map, const void* base, unsigned long long rows, int cols, int ld, int box_cols,
                               int box_rows, const char* who);
+
+// The larger limit on dynamic shared memory is a property of a kernel on ONE device: it is set the first time the kernel
+// is launched on each device, under a mutex (the entry points may be called from several threads).  A launcher keeps one
+// `SmemLimit` per kernel instantiation as a function-local static.
+constexpr int kMaxDevices = 64;
+struct SmemLimit {
+    std::mutex mutex;
+    bool raised[kMaxDevices] = {false};
+};
+template <typename Kernel>
+inline int raise_smem_limit(SmemLimit& state, Kernel kernel, size_t bytes, const char* who) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_error("%s: cannot tell the current device (%s)", who, cudaGetErrorString(e));
+        return -2;
+    }
+    std::lock_guard<std::mutex> lock(state.mutex);
+    if (state.raised[dev]) return 0;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) {
+        set_error("%s: cannot raise shared memory to %zu bytes: %s", who, bytes, cudaGetErrorString(e));
+        return -2;
+    }
+    state.raised[dev] = true;
+    return 0;
+}
 
 #define CIB_REQUIRE(cond, ...)            \
     do {                                  \

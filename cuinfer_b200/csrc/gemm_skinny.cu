@@ -328,15 +328,8 @@ static int launch_skinny(SkinnyArgs& a, int grid, int use_pdl, cudaStream_t stre
     if (a.res_in) smem += (size_t)a.K * 4;
     CIB_REQUIRE(smem <= 200 * 1024, "gemm_skinny: %d rows x K=%d need %zu bytes of shared memory", a.M, a.K, smem);
     auto kernel = skinny_gemm_kernel<MT, RT, KS, EPI, CS>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) {
-            set_error("gemm_skinny: cannot raise shared memory: %s", cudaGetErrorString(e));
-            return -2;
-        }
-        configured = true;
-    }
+    static SmemLimit limit;
+    if (int rc = raise_smem_limit(limit, kernel, 200 * 1024, "gemm_skinny")) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid * CS);
     cfg.blockDim = dim3(kSkWarps * 32);

@@ -344,15 +344,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtenso
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, F32OUT, TMA_STORE, SILU, PAIR>;
     constexpr int smem = TcSmem<BN, STAGES, PAIR>::kTotal;
     static_assert(smem <= 227 * 1024, "a CTA has 227 KB of shared memory");
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) {
-            set_error("gemm_tcgen05: cannot raise shared memory to %d: %s", smem, cudaGetErrorString(e));
-            return -2;
-        }
-        configured = true;
-    }
+    static SmemLimit limit;
+    if (int rc = raise_smem_limit(limit, kernel, smem, "gemm_tcgen05")) return rc;
     static int num_sms = 0;
     if (num_sms == 0) {
         int dev = 0;

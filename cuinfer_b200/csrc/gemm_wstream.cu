@@ -254,15 +254,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int l
     auto kernel = gemm_wstream_kernel<BX, STAGES, EPI>;
     constexpr int smem = Smem<BX, STAGES>::kTotal;
     static_assert(smem <= 227 * 1024, "a CTA has 227 KB of shared memory");
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) {
-            set_error("gemm_wstream: cannot raise shared memory to %d: %s", smem, cudaGetErrorString(e));
-            return -2;
-        }
-        configured = true;
-    }
+    static SmemLimit limit;
+    if (int rc = raise_smem_limit(limit, kernel, smem, "gemm_wstream")) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * splits);
     cfg.blockDim = dim3(192);
