@@ -37,6 +37,7 @@ struct SkinnyArgs {
     int act_stride;                                          // shared-memory row stride in elements
     const void* warm; unsigned long long warm_bytes;         // the weights of the kernel after this one (or null): fetched into L2
     int norm_w_offset;                                       // byte offset of the norm gains' copy in shared memory
+    int inbox_offset;                                        // CS > 1: byte offset of the first CTA's slots for the others' sums
 };
 
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
@@ -62,6 +63,8 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = lane & 3, qrow = lane >> 2;
     const int rt = warp % RT, ks = warp / RT;
+    // "this CTA runs": its shared memory may be written by the others of the cluster once all have said so
+    if (CS > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     // rows of this warp's tile
     int tile_row0;
@@ -202,9 +205,15 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     __syncthreads();
 
     // ---- main loop over this warp's k slice ----
-    float acc[MT][4];
+    // two accumulators per row tile, one for each half of a 32-k step: a warp's MMAs then form two chains of half the
+    // length instead of one (the k slices are short, so the chain's latency is most of the loop; four chains measured
+    // no better); summed at the end
+    float acc[MT][4], acc2[MT][4];
 #pragma unroll
-    for (int i = 0; i < MT; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    for (int i = 0; i < MT; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] = acc2[i][e] = 0.f;
+    }
     auto compute_chunk = [&](const uint4 (&wa)[kSkU], const uint4 (&wb)[kSkU], int step0) {
 #pragma unroll
         for (int u = 0; u < kSkU; ++u) {
@@ -217,7 +226,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
                     uint4 bv = make_uint4(0, 0, 0, 0);
                     if (k < a.K) bv = *reinterpret_cast<const uint4*>(s_act + (size_t)(nt * 8 + qrow) * a.act_stride + k);
                     mma_bf16_16816(acc[nt], a1, bv.x, bv.y);
-                    mma_bf16_16816(acc[nt], a2, bv.z, bv.w);
+                    mma_bf16_16816(acc2[nt], a2, bv.z, bv.w);
                 }
             }
         }
@@ -227,6 +236,11 @@ skinny_gemm_kernel(const SkinnyArgs a) {
         compute_chunk(waA, wbA, step0);
         load_chunk(waA, wbA, step0 + 2 * kSkU);
         compute_chunk(waB, wbB, step0 + kSkU);
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] += acc2[i][e];
     }
 
     // ---- sum the k slices (fixed order), then the epilogue ----
@@ -243,23 +257,28 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     }
     __syncthreads();
     if (CS > 1) {
-        // every CTA first sums its own slices into slot [0]; the others then add theirs into the first CTA's
-        // extra slots [KS + crank - 1] through distributed shared memory, and the first CTA sums in rank order
+        // every CTA sums its own slices; the others then write their sums into slots of the first CTA's shared memory
+        // that nothing else uses (so they need not wait for the first CTA to finish its loop), say so with a release
+        // and leave; the first CTA waits for them and sums in rank order
         cg::cluster_group cluster = cg::this_cluster();
         float* mine = red + (size_t)(KS + CS) * RT * 16 * kCols;          // [RT][16][kCols] sum of this CTA
+        float* inbox = reinterpret_cast<float*>(smem_raw + a.inbox_offset);   // [CS - 1][RT][16][kCols], used in the first CTA
         for (int idx = tid; idx < RT * 16 * kCols; idx += kSkWarps * 32) {
             float sum = 0.f;
 #pragma unroll
             for (int s = 0; s < KS; ++s) sum += red[(size_t)s * RT * 16 * kCols + idx];
             mine[idx] = sum;
         }
-        cluster.sync();
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");       // every CTA of the cluster runs
         if (crank != 0) {
-            float* dst = cluster.map_shared_rank(red + (size_t)(KS + crank) * RT * 16 * kCols, 0);
-            for (int idx = tid; idx < RT * 16 * kCols; idx += kSkWarps * 32) dst[idx] = mine[idx];
+            float* dst = cluster.map_shared_rank(inbox + (size_t)(crank - 1) * RT * 16 * kCols, 0);
+            for (int idx = tid; idx < RT * 16 * kCols; idx += kSkWarps * 32) dst[idx] = mine[idx];     // each thread copies what it summed
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            return;
         }
-        cluster.sync();
-        if (crank != 0) return;
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        __syncthreads();
         for (int idx = tid; idx < RT * 16 * kCols; idx += kSkWarps * 32) {
             const int token = idx / (RT * 16), nl = idx % (RT * 16);
             if (token >= a.M) continue;
@@ -267,7 +286,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
             const size_t e = ((size_t)t * 16 + r) * kCols + token;
             float sum = mine[e];
 #pragma unroll
-            for (int c = 1; c < CS; ++c) sum += red[(size_t)(KS + c) * RT * 16 * kCols + e];
+            for (int c = 1; c < CS; ++c) sum += inbox[(size_t)(c - 1) * RT * 16 * kCols + e];
             const int n = tile_block * RT * 16 + nl;
             if (n < a.N) {
                 if (EPI == kStoreF32) reinterpret_cast<float*>(a.out)[(size_t)token * a.ldo + n] = sum;
@@ -326,6 +345,9 @@ static int launch_skinny(SkinnyArgs& a, int grid, int use_pdl, cudaStream_t stre
     smem = (smem + 15) & ~size_t(15);
     a.norm_w_offset = (int)smem;
     if (a.res_in) smem += (size_t)a.K * 4;
+    smem = (smem + 15) & ~size_t(15);
+    a.inbox_offset = (int)smem;
+    if (CS > 1) smem += (size_t)(CS - 1) * RT * 16 * MT * 8 * 4;
     CIB_REQUIRE(smem <= 200 * 1024, "gemm_skinny: %d rows x K=%d need %zu bytes of shared memory", a.M, a.K, smem);
     auto kernel = skinny_gemm_kernel<MT, RT, KS, EPI, CS>;
     static SmemLimit limit;
