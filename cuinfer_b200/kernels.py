@@ -272,7 +272,7 @@ def paged_attention_decode_supports(head_dim: int, num_q_heads: int, num_kv_head
 decode_tma = os.environ.get("CUINFER_B200_DECODE_TMA", "1") != "0"
 
 
-DECODE_TMA_MIN_KEYS = 1024      # keys per CTA from which the TMA path of the decode kernel pays inside a step (measured)
+DECODE_TMA_MIN_KEYS = int(os.environ.get("CUINFER_B200_DECODE_TMA_MIN_KEYS", "1024"))      # keys per CTA from which the TMA path of the decode kernel pays inside a step (measured)
 
 
 def decode_tma_takes(page_size: int, head_dim: int, window: int) -> bool:
