@@ -23,6 +23,7 @@
 // Every mbarrier wait is bounded; on a time-out the kernel raises the error flag, stops, frees its tensor memory
 // and returns.
 #include "common.cuh"
+#include "mma_utils.cuh"
 #include "tcgen05_utils.cuh"
 
 namespace cib {
@@ -131,6 +132,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
+    // everything so far read only what the host wrote for this step; queries, keys and values come from the kernel before
+    griddep_launch();
+    griddep_wait();
     const uint32_t tmem = *tmem_slot;
     const int r = s_req;
     const bool active = r < num_requests;
@@ -467,9 +471,13 @@ extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int
     static SmemLimit limit;
     if (int rc = raise_smem_limit(limit, fa::attention_tcgen05_kernel, fa::kSmemBytes, "attention_tcgen05")) return rc;
     dim3 grid(nkv, num_tiles);
-    fa::attention_tcgen05_kernel<<<grid, fa::kThreads, fa::kSmemBytes, stream>>>(
-        kv_map, num_pages, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, page_size, block_table, table_stride,
-        query_start_loc, seq_lens, num_requests, nq, nkv, scale * 1.4426950408889634f, window, error_flag);
-    CIB_LAUNCH_CHECK("attention_tcgen05");
+    cudaError_t e = launch_pdl(fa::attention_tcgen05_kernel, grid, dim3(fa::kThreads), (size_t)fa::kSmemBytes, stream, prompt_pdl(),
+                               kv_map, num_pages, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, page_size,
+                               block_table, table_stride, query_start_loc, seq_lens, num_requests, nq, nkv,
+                               scale * 1.4426950408889634f, window, error_flag);
+    if (e != cudaSuccess) {
+        set_error("attention_tcgen05: launch failed: %s", cudaGetErrorString(e));
+        return -2;
+    }
     return 0;
 }

@@ -46,5 +46,11 @@ int encode_tensor_map_bf16_2d(void* map, const void* base, unsigned long long ro
 
 extern "C" const char* cib_last_error() { return cib::g_error; }
 
+namespace cib {
+static int g_prompt_pdl = 0;
+bool prompt_pdl() { return g_prompt_pdl != 0; }
+}  // namespace cib
+extern "C" void cib_set_prompt_pdl(int on) { cib::g_prompt_pdl = on; }
+
 // Bumped whenever an exported signature changes, so that a stale library is rebuilt, not misused.
 extern "C" int cib_abi_version() { return 2; }

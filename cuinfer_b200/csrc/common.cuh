@@ -22,6 +22,12 @@ constexpr int kWarp = 32;
 // ---- error reporting -------------------------------------------------------------------
 void set_error(const char* fmt, ...);
 
+// Whether the kernels of prompt-sized steps (tcgen05 GEMM and attention, row-wise norm) are launched with the
+// programmatic-dependent-launch attribute, so that a kernel's set-up runs under the tail of the kernel before it
+// (`cib_set_prompt_pdl`; off until the host switches it on).  Each of them waits for that kernel before it reads or
+// writes anything a kernel produces.
+bool prompt_pdl();
+
 // A 2-D tensor map over bfloat16 rows (`cols` elements, `ld` elements apart) with boxes of box_cols x box_rows,
 // 128-byte swizzle, zero fill outside.  `map` points at a CUtensorMap (kept opaque here so that only the files that
 // issue TMA copies include the driver header).  0, or -1 with the error text set.

@@ -6,6 +6,7 @@
 // Unlike those, every size is a run-time parameter, the residual stream is kept in 32 bits, and the
 // add, the norm and the store of the new residual are one pass over the row.
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 namespace cib {
 
@@ -106,6 +107,8 @@ template <typename TD, typename TO, int CH>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ delta, AnyVec weight, float eps,
                         TO* __restrict__ out, int hidden, int rows) {
+    griddep_launch();
+    griddep_wait();          // residual and delta come from the kernels before this one
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= rows) return;
@@ -229,9 +232,10 @@ static void launch_add_rmsnorm(float* residual, const void* delta, AnyVec w, flo
     if (hidden % 4 == 0 && rows >= 256 && hidden <= 2048) {
         const int ch = (hidden + 127) / 128;
         const dim3 grid((rows + 7) / 8);
-        if (ch <= 4) add_rmsnorm_rows_kernel<TD, TO, 4><<<grid, 256, 0, stream>>>(residual, (const TD*)delta, w, eps, (TO*)out, hidden, rows);
-        else if (ch <= 8) add_rmsnorm_rows_kernel<TD, TO, 8><<<grid, 256, 0, stream>>>(residual, (const TD*)delta, w, eps, (TO*)out, hidden, rows);
-        else add_rmsnorm_rows_kernel<TD, TO, 16><<<grid, 256, 0, stream>>>(residual, (const TD*)delta, w, eps, (TO*)out, hidden, rows);
+        const bool pdl = prompt_pdl();
+        if (ch <= 4) launch_pdl(add_rmsnorm_rows_kernel<TD, TO, 4>, dim3(grid), dim3(256), 0, stream, pdl, residual, (const TD*)delta, w, eps, (TO*)out, hidden, rows);
+        else if (ch <= 8) launch_pdl(add_rmsnorm_rows_kernel<TD, TO, 8>, dim3(grid), dim3(256), 0, stream, pdl, residual, (const TD*)delta, w, eps, (TO*)out, hidden, rows);
+        else launch_pdl(add_rmsnorm_rows_kernel<TD, TO, 16>, dim3(grid), dim3(256), 0, stream, pdl, residual, (const TD*)delta, w, eps, (TO*)out, hidden, rows);
     } else if (hidden % 4 == 0) {
         add_rmsnorm_kernel<TD, TO, 4><<<rows, norm_threads(hidden, 4), 0, stream>>>(residual, (const TD*)delta, w, eps, (TO*)out, hidden);
     } else {

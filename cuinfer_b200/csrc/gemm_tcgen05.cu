@@ -16,6 +16,7 @@
 // Rows beyond M, features beyond N and the tail of K read as zeros (TMA out-of-bounds fill) and are not stored.
 // Every mbarrier wait is bounded: if a limit is hit the kernel raises a flag in global memory, stops issuing,
 // drains what it started, frees its tensor memory and returns, so a fault in this kernel cannot hang the device.
+#include "mma_utils.cuh"
 #include "tcgen05_utils.cuh"
 
 #include <stdlib.h>
@@ -89,6 +90,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (PAIR) cluster_sync_all();          // the other CTA's barriers exist before anything arrives on them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up (barriers, tensor memory) may run under the tail of the kernel before this one; its results may not be read
+    // nor this kernel's written before it has ended
+    griddep_launch();
+    griddep_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -357,8 +362,11 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtenso
     const int tiles = ((n_out + out_cols - 1) / out_cols) * ((M + tile_rows - 1) / tile_rows);
     if (!PAIR) {
         dim3 grid(tiles < num_sms ? tiles : num_sms);
-        kernel<<<grid, 192, smem, stream>>>(ma, mw, mo, out, ldo, M, N, K, up_offset, error_flag);
-        CIB_LAUNCH_CHECK("gemm_tcgen05");
+        cudaError_t e = launch_pdl(kernel, grid, dim3(192), (size_t)smem, stream, prompt_pdl(), ma, mw, mo, out, ldo, M, N, K, up_offset, error_flag);
+        if (e != cudaSuccess) {
+            set_error("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
+            return -2;
+        }
         return 0;
     }
     // clusters of two CTAs, one pair per tile at a time
@@ -368,13 +376,15 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtenso
     cfg.blockDim = dim3(192);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = prompt_pdl() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mw, mo, out, ldo, M, N, K, up_offset, error_flag);
     if (e != cudaSuccess) {
         set_error("gemm_tcgen05: launch of CTA pairs failed: %s", cudaGetErrorString(e));

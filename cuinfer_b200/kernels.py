@@ -50,6 +50,9 @@ def library() -> ctypes.CDLL:
             ) from exc
         lib.cib_last_error.restype = ctypes.c_char_p
         _declare(lib)
+        lib.cib_set_prompt_pdl.argtypes = [ctypes.c_int]
+        lib.cib_set_prompt_pdl.restype = None
+        lib.cib_set_prompt_pdl(1 if os.environ.get("CUINFER_B200_PROMPT_PDL", "1") != "0" and os.environ.get("CUINFER_B200_PDL", "1") != "0" else 0)
         _lib_handle = lib
         return lib
 
