@@ -17,7 +17,7 @@ from __future__ import annotations
 import gc
 import weakref
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -139,8 +139,13 @@ class ModelRunner:
         return int(pages)
 
     def _activation_bytes(self) -> int:
-        """What a step of a full token budget allocates beside weights and cache; the parts say how much."""
-        return self.model.workspace_bytes(self.config.max_num_scheduled_tokens, self.config.max_num_seqs)
+        """What a step of a full token budget allocates beside weights and cache, and what the captured steps keep
+        (each graph has a pool of its own for the intermediates of its sizes); the parts say how much."""
+        step = self.model.workspace_bytes(self.config.max_num_scheduled_tokens, self.config.max_num_seqs)
+        if not self.config.enable_cuda_graph:
+            return step
+        captured = min(self.config.max_num_scheduled_tokens, self.STEP_GRAPH_MAX_TOKENS)
+        return step + self.STEP_GRAPH_LIMIT * self.model.workspace_bytes(captured, self.config.max_num_seqs) // 2
 
     # ---- requests ------------------------------------------------------------------------------------
     def reserve(self, request_id: Hashable, num_new_tokens: int) -> bool:
@@ -208,15 +213,22 @@ class ModelRunner:
             seen.add(rid)
 
     def build_context(self, entries: Sequence[StepEntry], table_stride: Optional[int] = None,
-                      arena: Optional[torch.Tensor] = None):
+                      arena: Optional[torch.Tensor] = None, pad: Optional[Tuple[int, int, int]] = None):
         """Pack the batch, copy it to the device and return ``(StepContext, logits_indices tensor)``.
-        ``arena``: the device buffer to copy into (a captured step's own); default: the runner's."""
+        ``arena``: the device buffer to copy into (a captured step's own); default: the runner's.
+        ``pad = (tokens, requests, wanted rows)``: lay the batch out for that many — the sizes a captured step was
+        recorded with.  The tokens beyond the batch's own belong to one more request that holds no pages and writes
+        none (positions 0, 1, ...; slot -1; empty block table), further requests bring no tokens, and the wanted rows
+        beyond the batch's own point at row 0; the caller drops what comes out of them."""
         mgr = self.manager
-        R = len(entries)
+        R_live = len(entries)
         lens = [len(e.tokens) for e in entries]
         starts = [mgr.num_tokens(e.request_id) for e in entries]
-        T = sum(lens)
-        S = sum(len(e.want) for e in entries)
+        T_live = sum(lens)
+        S_live = sum(len(e.want) for e in entries)
+        T, R, S = pad if pad is not None else (T_live, R_live, S_live)
+        if T < T_live or S < S_live or R < R_live + (1 if T > T_live else 0):
+            raise StepError(f"a step of {T_live} tokens, {R_live} requests, {S_live} wanted rows does not fit the sizes {pad}")
         G = len(self.groups)
         P = table_stride or max(1, max(len(mgr.block_table(e.request_id, g)) for e in entries for g in range(G))) if G else 1
         total = 3 * T + (R + 1) + 2 * R + S + G * (T + R * P)
@@ -241,6 +253,16 @@ class ModelRunner:
         qsl[0] = 0
         t0 = 0
         w0 = 0
+        if pad is not None:                      # the padding: no token ids but 0, one request for the spare tokens
+            tok[T_live:] = 0
+            pos[T_live:] = np.arange(T - T_live, dtype=np.int32)
+            treq[T_live:] = R_live if R > R_live else 0
+            qsl[R_live + 1:] = T
+            sl[R_live:] = 0
+            if R > R_live:
+                sl[R_live] = T - T_live
+            slots[R_live:] = -1
+            want[S_live:] = 0
         for r, e in enumerate(entries):
             n = lens[r]
             tok[t0:t0 + n] = np.asarray(e.tokens, dtype=np.int32)
@@ -258,6 +280,7 @@ class ModelRunner:
             sm, o_sm = take(T)
             bt, o_bt = take(R * P)
             bt[:] = -1
+            sm[T_live:] = -1
             t0 = 0
             for r, e in enumerate(entries):
                 table = mgr.block_table(e.request_id, g)
@@ -294,8 +317,8 @@ class ModelRunner:
             query_start_loc=dev[o_qsl:o_qsl + R + 1], seq_lens=dev[o_sl:o_sl + R], state_slots=dev[o_slots:o_slots + R],
             query_start_loc_host=[int(v) for v in qsl], seq_lens_host=[int(v) for v in sl],
             state_slots_host=[int(v) for v in slots],
-            max_query_len=max(lens), max_seq_len=max(int(v) for v in sl), groups=groups,
-            decode_only=all(n == 1 for n in lens),
+            max_query_len=max(max(lens), T - T_live), max_seq_len=max(int(v) for v in sl), groups=groups,
+            decode_only=pad is None and all(n == 1 for n in lens),
         )
         for run, (src, writes) in self._run_cache.items():
             ctx.kv[run] = PagedKV(self.storage.run_cache[src], groups[self.storage.run_group[src]], writes)
@@ -322,14 +345,28 @@ class ModelRunner:
         self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
 
-    # ---- prompt-sized steps whose shape repeats, as CUDA graphs -------------------------------------------
+    # ---- steps that are not all single tokens, as CUDA graphs ----------------------------------------------------
     # Launching the ~9 kernels of a layer one by one costs the host about as long as they run (each launch is a few
-    # microseconds of Python, a kernel of a 2048-token portion 5-50 us), so a step whose shape — the number of tokens
-    # and of wanted logits of every entry — has been seen before is captured once and replayed from then on.  Chunked
-    # prefill at the token budget and benchmarks repeat shapes; other steps run eagerly as before.
-    STEP_GRAPH_MIN_TOKENS = 256
-    STEP_GRAPH_MAX_ENTRIES = 16
-    STEP_GRAPH_LIMIT = 4
+    # microseconds of Python, a kernel of a 2048-token portion 5-50 us; a step of 31 decoded tokens beside 48 prompt
+    # tokens took 6.9 ms launch by launch).  Such a step is therefore padded to a bucket of (tokens, requests, wanted
+    # rows) and run as a graph captured for the bucket: the first time a bucket comes it runs launch by launch, the
+    # second time it is captured, from then on replayed.  The spare tokens belong to a request without pages (see
+    # ``build_context``); nothing of them reaches the caller.
+    # Above STEP_GRAPH_MAX_TOKENS a step's kernels run longer than the host needs to launch them, and a graph of that
+    # size takes tens of milliseconds to capture and hundreds of megabytes to keep: those steps stay eager.
+    STEP_GRAPH_MIN_TOKENS = 32
+    STEP_GRAPH_MAX_TOKENS = 4096
+    STEP_GRAPH_MAX_ENTRIES = 255
+    STEP_GRAPH_LIMIT = 8
+
+    @staticmethod
+    def step_bucket(lens: Sequence[int], wants: Sequence[int]) -> Tuple[int, int, int]:
+        """(tokens, requests, wanted rows) of the captured step that a batch of these query lengths and numbers of
+        wanted rows runs in: tokens rounded up in steps of an eighth of their size (at least 16), requests to a power
+        of two with room for the request that takes the spare tokens, wanted rows to a power of two."""
+        T, R, S = sum(lens), len(lens), sum(wants)
+        step = max(16, 1 << max(0, (T - 1).bit_length() - 4))        # 2048 -> 128, 2049 -> 256: at most an eighth spare
+        return -(-T // step) * step, 1 << R.bit_length(), (1 << (S - 1).bit_length()) if S else 0
 
     def _step_graph(self, entries: Sequence[StepEntry]) -> Optional["StepGraph"]:
         if not self.config.enable_cuda_graph or len(entries) > self.STEP_GRAPH_MAX_ENTRIES or not self.model.capturable:
@@ -337,9 +374,12 @@ class ModelRunner:
         lens = tuple(len(e.tokens) for e in entries)
         if sum(lens) < self.STEP_GRAPH_MIN_TOKENS:
             return None
-        key = (lens, tuple(len(e.want) for e in entries))
+        key = self.step_bucket(lens, [len(e.want) for e in entries])
+        if key[0] > self.STEP_GRAPH_MAX_TOKENS:
+            return None
         graph = self._step_graphs.get(key)
         if graph is not None:
+            graph.uses += 1
             return graph
         if len(self._step_seen) > 4096:
             self._step_seen.clear()
@@ -347,8 +387,14 @@ class ModelRunner:
         self._step_seen[key] = seen
         if seen < 2:
             return None
-        while len(self._step_graphs) >= self.STEP_GRAPH_LIMIT:
-            self._step_graphs.pop(next(iter(self._step_graphs)))          # the oldest; its memory pool goes with it
+        if len(self._step_graphs) >= self.STEP_GRAPH_LIMIT:
+            # A graph makes room only for a bucket that has come more often than the graph was used since it was made:
+            # a workload that cycles through more buckets than are kept then runs the rarer ones launch by launch
+            # instead of capturing anew every time (a capture costs as much as tens of steps).
+            least = min(self._step_graphs, key=lambda k: self._step_graphs[k].uses)
+            if self._step_graphs[least].uses >= seen:
+                return None
+            self._step_graphs.pop(least)                                  # its memory pool goes with it
         graph = StepGraph(self, key)
         self._step_graphs[key] = graph
         return graph
@@ -590,24 +636,28 @@ class DecodeGraph:
 
 
 class StepGraph:
-    """A CUDA graph of one step of a fixed shape: the same numbers of tokens and of wanted logits per entry.
+    """A CUDA graph of one step of fixed sizes: so many tokens, requests and wanted rows (``ModelRunner.step_bucket``).
 
-    Positions, cache slots, block tables, token ids and the indices of the wanted rows are data in the graph's own
-    device arena (packed by ``ModelRunner.build_context`` as for an eager step and refreshed by one copy), so any
-    requests of these lengths at any positions replay it.  What shapes a launch — the attention kernels' tile counts —
-    depends on the query lengths only, which are the key.  The first use runs the step eagerly (that is its result)
-    and then records it; later uses replay.  The logits tensor is overwritten by the next replay.
+    Positions, cache slots, block tables, token ids, the requests' boundaries and the indices of the wanted rows are
+    data in the graph's own device arena (packed by ``ModelRunner.build_context`` as for an eager step, padded to the
+    graph's sizes, and refreshed by one copy), so any batch that fits the sizes replays it.  What shapes a launch — the
+    attention kernels' tile counts — is sized for the worst split of the tokens over the requests
+    (``StepContext.launch_query_lens``); CTAs beyond the batch's own tiles find no request and leave.  The first use
+    runs the step eagerly (that is its result) and then records it; later uses replay.  The logits tensor is
+    overwritten by the next replay.
     """
 
-    def __init__(self, runner: "ModelRunner", key: tuple) -> None:
+    def __init__(self, runner: "ModelRunner", key: Tuple[int, int, int]) -> None:
         self._runner = weakref.ref(runner)
-        lens, wants = key
-        T, R, S, G = sum(lens), len(lens), sum(wants), len(runner.groups)
+        self.key = key
+        T, R, S = key
+        G = len(runner.groups)
         self.stride = (runner.max_model_len + runner.page_size - 1) // runner.page_size
         total = 3 * T + (R + 1) + 2 * R + S + G * (T + R * self.stride)
         self.arena = torch.empty(total, dtype=torch.int32, device=runner.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
+        self.uses = 1                            # times the runner has picked this graph (it decides what to drop by it)
 
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         from .. import kernels
@@ -615,16 +665,22 @@ class StepGraph:
         runner = self._runner()
         if runner is None:
             raise RuntimeError("the engine of this step graph is gone")
-        ctx, want = runner.build_context(entries, table_stride=self.stride, arena=self.arena)
-        # what a replay cannot know: only the query lengths (the graph's key) stay on the host side of the context
+        T, R, S = self.key
+        wanted = sum(len(e.want) for e in entries)
+        ctx, want = runner.build_context(entries, table_stride=self.stride, arena=self.arena, pad=self.key)
+        # what a replay cannot know stays off the host side of the context: launches are sized for the worst split of
+        # the graph's tokens over its requests (one more 128-row tile than the tokens fill, one tile per further request)
+        ctx.query_start_loc_host = None
         ctx.seq_lens_host = None
         ctx.state_slots_host = None
+        ctx.launch_query_lens = [T + 128] + [1] * (R - 1)
+        ctx.max_query_len = T
         ctx.max_seq_len = runner.max_model_len
         if self.graph is not None:
             self.graph.replay()
             kernels.note_flagged_launch(replayed=True)
             runner.step_graph_replays += 1
-            return self.logits
+            return self.logits[:wanted]
 
         def forward() -> torch.Tensor:
             stream = runner.model.forward(ctx)
@@ -639,4 +695,4 @@ class StepGraph:
         with torch.cuda.graph(graph, capture_error_mode="relaxed"):
             self.logits = forward()              # recorded, not run
         self.graph = graph
-        return logits
+        return logits[:wanted]

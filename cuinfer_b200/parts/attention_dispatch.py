@@ -35,14 +35,12 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: Step
         return
     if qkv.dtype == torch.bfloat16 and not _FORCE_MMA and kernels.attention_tcgen05_supports(
             head_dim, num_heads, num_kv_heads, kv.group.page_size) and out.stride(0) % 8 == 0 and qkv.stride(0) % 8 == 0:
-        starts = ctx.query_start_loc_host
-        lens = [starts[i + 1] - starts[i] for i in range(ctx.num_requests)]
+        lens = ctx.query_lens_for_launch()
         kernels.attention_tcgen05(qkv, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens, lens,
                                   num_heads, num_kv_heads, head_dim, scale, window)
         return
     if qkv.dtype == torch.bfloat16 and kernels.paged_attention_prefill_supports(head_dim, num_heads, num_kv_heads):
-        starts = ctx.query_start_loc_host
-        lens = [starts[i + 1] - starts[i] for i in range(ctx.num_requests)]
+        lens = ctx.query_lens_for_launch()
         kernels.paged_attention_prefill(qkv, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
                                         lens, num_heads, num_kv_heads, head_dim, scale, window)
         return

@@ -116,9 +116,10 @@ CUTS = {
 @pytest.mark.parametrize("cut", sorted(CUTS))
 def test_cuts_through_cuda_graphs(model_folders, name, dtype, cut, tmp_path, monkeypatch):
     """The four cuts again, through the paths generation really takes: every step of single tokens is a replayed
-    decode graph (padding rows, incremental block-table upload), every other step whose shape has come back is a
-    replayed step graph.  The trace runs three times through one runner — shapes are captured the second time and
-    replayed the third — and the logits of the last pass are compared, at the same tolerance as eager steps."""
+    decode graph (padding rows, incremental block-table upload), every other step is padded to a bucket of sizes and,
+    once the bucket has come back, a replayed step graph (spare tokens in a request without pages, spare requests,
+    spare wanted rows).  The trace runs three times through one runner and the logits of the last pass, all from
+    replays, are compared at the same tolerance as eager steps."""
     from cuinfer_b200.engine.runner import ModelRunner
     monkeypatch.setattr(ModelRunner, "STEP_GRAPH_MIN_TOKENS", 2)
     monkeypatch.setattr(ModelRunner, "STEP_GRAPH_LIMIT", 64)
@@ -137,8 +138,10 @@ def test_cuts_through_cuda_graphs(model_folders, name, dtype, cut, tmp_path, mon
     other = len(steps) - decode_steps
     shapes = {tuple((len(e["tokens"]), len(e["want"])) for e in st["entries"]) for st in steps
               if not all(len(e["tokens"]) == 1 and e["want"] == [0] for e in st["entries"])}
-    # pass 1 runs every such step eagerly, pass 2 captures each shape at its first return, pass 3 replays everything
-    assert runner.step_graph_replays >= other and len(runner._step_graphs) == len(shapes)
+    buckets = {ModelRunner.step_bucket([n for n, _ in shape], [w for _, w in shape]) for shape in shapes}
+    # a bucket of sizes runs launch by launch when it first comes, is captured when it comes back (in pass 2 at the
+    # latest), and pass 3 replays everything
+    assert runner.step_graph_replays >= other and len(runner._step_graphs) == len(buckets)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
