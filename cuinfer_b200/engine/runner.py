@@ -110,6 +110,7 @@ class ModelRunner:
         self._step_graphs: Dict[tuple, "StepGraph"] = {}     # shape of a prompt-sized step -> graph (a few, oldest dropped)
         self._step_seen: Dict[tuple, int] = {}
         self.step_graph_replays = 0
+        self.step_graph_captures = 0
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -388,7 +389,7 @@ class ModelRunner:
         if seen < 2:
             return None
         if len(self._step_graphs) >= self.STEP_GRAPH_LIMIT:
-            # A graph makes room only for a bucket that has come more often than the graph was used since it was made:
+            # A graph makes room only for a bucket that has come more often than the graph's own:
             # a workload that cycles through more buckets than are kept then runs the rarer ones launch by launch
             # instead of capturing anew every time (a capture costs as much as tens of steps).
             least = min(self._step_graphs, key=lambda k: self._step_graphs[k].uses)
@@ -396,6 +397,7 @@ class ModelRunner:
                 return None
             self._step_graphs.pop(least)                                  # its memory pool goes with it
         graph = StepGraph(self, key)
+        graph.uses = seen                        # it starts level with how often its bucket has come
         self._step_graphs[key] = graph
         return graph
 
@@ -695,4 +697,5 @@ class StepGraph:
         with torch.cuda.graph(graph, capture_error_mode="relaxed"):
             self.logits = forward()              # recorded, not run
         self.graph = graph
+        runner.step_graph_captures += 1
         return logits[:wanted]

@@ -54,3 +54,24 @@ def test_l2_hints_are_given_for_small_weights_only():
     small = torch.empty(1024, 1024, dtype=torch.bfloat16)
     large = torch.empty(kernels.L2_HINT_MAX_BYTES // 2 + 8, dtype=torch.bfloat16)
     assert kernels._l2_hint(small) is small and kernels._l2_hint(large) is None and kernels._l2_hint(None) is None
+
+
+def test_step_buckets_hold_their_batches_with_little_to_spare():
+    """The sizes a step is padded to before it runs as a captured graph: never smaller than the batch, one request to
+    spare for the spare tokens, at most an eighth (or 15) more tokens, and few distinct buckets."""
+    from cuinfer_b200.engine.runner import ModelRunner
+
+    rnd = random.Random(1)
+    seen = set()
+    for _ in range(3000):
+        R = rnd.choice([1, 1, 2, 3, 8, 17, 33, 100, 255])
+        lens = [rnd.choice([1, 1, 1, 2, 7, 60, 500, 2000]) for _ in range(R)]
+        wants = [rnd.choice([0, 1, 1, 2]) for _ in range(R)]
+        T, S = sum(lens), sum(wants)
+        Tb, Rb, Sb = ModelRunner.step_bucket(lens, wants)
+        assert T <= Tb <= max(T + 15, T + T // 8 + 1) and Tb % 16 == 0
+        assert R < Rb <= 2 * R and Rb & (Rb - 1) == 0
+        assert S <= Sb <= max(2 * S - 1, 0) and Sb & (Sb - 1) == 0
+        seen.add(Tb)
+    assert len(seen) < 120
+    assert ModelRunner.step_bucket([2048], [1]) == (2048, 2, 1) and ModelRunner.step_bucket([8192], [1])[0] == 8192

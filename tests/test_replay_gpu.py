@@ -218,3 +218,44 @@ def test_trace_run_program(model_folders, tmp_path):
     assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {st['step']}" for st in steps]
     got = traces.collect(steps, str(out), cfg["vocab_size"])
     traces.compare_with_plain(folder, requests, got, TOLERANCE["float32"])
+
+
+def test_step_graphs_pad_to_their_bucket_and_do_not_thrash(model_folders, monkeypatch):
+    """Steps of other shapes in one bucket replay one captured graph and give the logits of eager steps; with room
+    for two graphs and three buckets in turn, the third keeps running launch by launch instead of pushing a graph out
+    every time it comes (a capture costs as much as tens of steps)."""
+    from cuinfer_b200.engine import replay
+    from cuinfer_b200.engine.runner import ModelRunner, StepEntry
+
+    monkeypatch.setattr(ModelRunner, "STEP_GRAPH_MIN_TOKENS", 2)
+    monkeypatch.setattr(ModelRunner, "STEP_GRAPH_LIMIT", 2)
+    folders, cfg, block = model_folders["D"]
+    graphed = replay.make_runner(folders["bfloat16"], "bfloat16", 4096, block, cuda_graph=True)
+    eager = replay.make_runner(folders["bfloat16"], "bfloat16", 4096, block, cuda_graph=False)
+    shapes = {"a": [[33, 5, 1], [30, 1, 9], [36, 2, 1]],         # bucket (48, 4, 4): 9, 8 and 9 spare tokens
+              "b": [[70], [66]],                                   # bucket (80, 2, 1)
+              "c": [[100, 3], [97, 12]]}                           # bucket (112, 4, 2)
+    serial = 0
+    worst = 0.0
+    for round_ in range(6):
+        for name in "abc":
+            lens = shapes[name][round_ % len(shapes[name])]
+            ids = [f"{name}{round_}_{i}" for i in range(len(lens))]
+            tokens = [random_tokens(cfg["vocab_size"], n, 900 + serial + i) for i, n in enumerate(lens)]
+            serial += 7
+            out = []
+            for runner in (graphed, eager):
+                entries = [StepEntry(i, t, [len(t) - 1]) for i, t in zip(ids, tokens)]
+                for e in entries:
+                    assert runner.reserve(e.request_id, len(e.tokens))
+                out.append(runner.step(entries).float().cpu())
+                for i in ids:
+                    runner.release(i)
+                runner.manager.check()
+            scale = float(out[1].abs().max())
+            worst = max(worst, float((out[0] - out[1]).abs().max()) / scale)
+    assert worst <= 2e-2, worst          # same kernels on the same rows; only the row count of the products differs
+    # "a" and "b" are captured when they come the second time; "c" finds both places taken by graphs that are used as
+    # often as it comes, and never pushes one out
+    assert len(graphed._step_graphs) == 2 and graphed.step_graph_captures == 2
+    assert graphed.step_graph_replays == 2 * 4
