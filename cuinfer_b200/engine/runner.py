@@ -111,6 +111,8 @@ class ModelRunner:
         self._step_seen: Dict[tuple, int] = {}
         self.step_graph_replays = 0
         self.step_graph_captures = 0
+        self._step_pool = None                   # the memory pool all step graphs record into, and the stream they record on
+        self._step_stream = None
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -146,7 +148,9 @@ class ModelRunner:
         if not self.config.enable_cuda_graph:
             return step
         captured = min(self.config.max_num_scheduled_tokens, self.STEP_GRAPH_MAX_TOKENS)
-        return step + self.STEP_GRAPH_LIMIT * self.model.workspace_bytes(captured, self.config.max_num_seqs) // 2
+        # the step graphs share one pool, which grows to the largest of them; their results (logits) stay allocated
+        logits = self.STEP_GRAPH_LIMIT * 64 * self.vocab_size * 4
+        return step + self.model.workspace_bytes(captured, self.config.max_num_seqs) + logits
 
     # ---- requests ------------------------------------------------------------------------------------
     def reserve(self, request_id: Hashable, num_new_tokens: int) -> bool:
@@ -358,16 +362,18 @@ class ModelRunner:
     STEP_GRAPH_MIN_TOKENS = 32
     STEP_GRAPH_MAX_TOKENS = 4096
     STEP_GRAPH_MAX_ENTRIES = 255
-    STEP_GRAPH_LIMIT = 8
+    STEP_GRAPH_LIMIT = 32
 
     @staticmethod
     def step_bucket(lens: Sequence[int], wants: Sequence[int]) -> Tuple[int, int, int]:
         """(tokens, requests, wanted rows) of the captured step that a batch of these query lengths and numbers of
         wanted rows runs in: tokens rounded up in steps of an eighth of their size (at least 16), requests to a power
-        of two with room for the request that takes the spare tokens, wanted rows to a power of two."""
+        of two with room for the request that takes the spare tokens, wanted rows to as many as there are requests
+        (a row each is the usual case, and the output head's time hardly depends on them) or the next power of two."""
         T, R, S = sum(lens), len(lens), sum(wants)
         step = max(16, 1 << max(0, (T - 1).bit_length() - 4))        # 2048 -> 128, 2049 -> 256: at most an eighth spare
-        return -(-T // step) * step, 1 << R.bit_length(), (1 << (S - 1).bit_length()) if S else 0
+        Rb = 1 << R.bit_length()
+        return -(-T // step) * step, Rb, (max(Rb, 1 << (S - 1).bit_length())) if S else 0
 
     def _step_graph(self, entries: Sequence[StepEntry]) -> Optional["StepGraph"]:
         if not self.config.enable_cuda_graph or len(entries) > self.STEP_GRAPH_MAX_ENTRIES or not self.model.capturable:
@@ -646,7 +652,8 @@ class StepGraph:
     attention kernels' tile counts — is sized for the worst split of the tokens over the requests
     (``StepContext.launch_query_lens``); CTAs beyond the batch's own tiles find no request and leave.  The first use
     runs the step eagerly (that is its result) and then records it; later uses replay.  The logits tensor is
-    overwritten by the next replay.
+    overwritten by the next replay of this or any other step graph of the runner (they share one memory pool); the
+    engine samples from it, on the same stream, before it launches another step.
     """
 
     def __init__(self, runner: "ModelRunner", key: Tuple[int, int, int]) -> None:
@@ -691,11 +698,31 @@ class StepGraph:
             return torch.empty((0, runner.vocab_size), dtype=torch.float32, device=runner.device)
 
         logits = forward()                       # this step's result; also creates what must exist before a capture
-        torch.cuda.synchronize(runner.device)
-        gc.collect()                             # see DecodeGraph.capture
+        # Recorded by hand rather than under ``torch.cuda.graph``: that empties the allocator's cache and collects
+        # garbage on the way in, which made a capture cost as much as twenty steps and the steps after it pay for fresh
+        # device memory.  All step graphs record into one memory pool: they never run at the same time, so the
+        # intermediates of one may lie where another's do (a graph's result stays allocated, it is not an
+        # intermediate).  The cyclic collector is off meanwhile: it could destroy another engine's graph inside the
+        # recording (see DecodeGraph.capture); relaxed mode lets the allocator work on other threads.
+        if runner._step_pool is None:
+            runner._step_pool = torch.cuda.graph_pool_handle()
+            runner._step_stream = torch.cuda.Stream(runner.device)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, capture_error_mode="relaxed"):
-            self.logits = forward()              # recorded, not run
+        side = runner._step_stream
+        side.wait_stream(torch.cuda.current_stream(runner.device))
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.stream(side):
+                graph.capture_begin(pool=runner._step_pool, capture_error_mode="relaxed")
+                try:
+                    self.logits = forward()      # recorded, not run
+                finally:
+                    graph.capture_end()
+        finally:
+            if collecting:
+                gc.enable()
+        torch.cuda.current_stream(runner.device).wait_stream(side)
         self.graph = graph
         runner.step_graph_captures += 1
         return logits[:wanted]

@@ -71,7 +71,7 @@ def test_step_buckets_hold_their_batches_with_little_to_spare():
         Tb, Rb, Sb = ModelRunner.step_bucket(lens, wants)
         assert T <= Tb <= max(T + 15, T + T // 8 + 1) and Tb % 16 == 0
         assert R < Rb <= 2 * R and Rb & (Rb - 1) == 0
-        assert S <= Sb <= max(2 * S - 1, 0) and Sb & (Sb - 1) == 0
+        assert S <= Sb <= max(2 * S - 1, Rb if S else 0) and Sb & (Sb - 1) == 0
         seen.add(Tb)
     assert len(seen) < 120
-    assert ModelRunner.step_bucket([2048], [1]) == (2048, 2, 1) and ModelRunner.step_bucket([8192], [1])[0] == 8192
+    assert ModelRunner.step_bucket([2048], [1]) == (2048, 2, 2) and ModelRunner.step_bucket([8192], [1])[0] == 8192

@@ -233,8 +233,8 @@ def test_step_graphs_pad_to_their_bucket_and_do_not_thrash(model_folders, monkey
     graphed = replay.make_runner(folders["bfloat16"], "bfloat16", 4096, block, cuda_graph=True)
     eager = replay.make_runner(folders["bfloat16"], "bfloat16", 4096, block, cuda_graph=False)
     shapes = {"a": [[33, 5, 1], [30, 1, 9], [36, 2, 1]],         # bucket (48, 4, 4): 9, 8 and 9 spare tokens
-              "b": [[70], [66]],                                   # bucket (80, 2, 1)
-              "c": [[100, 3], [97, 12]]}                           # bucket (112, 4, 2)
+              "b": [[70], [66]],                                   # bucket (80, 2, 2)
+              "c": [[100, 3], [97, 12]]}                           # bucket (112, 4, 4)
     serial = 0
     worst = 0.0
     for round_ in range(6):
