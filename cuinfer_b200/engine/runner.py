@@ -111,8 +111,8 @@ class ModelRunner:
         self._step_seen: Dict[tuple, int] = {}
         self.step_graph_replays = 0
         self.step_graph_captures = 0
-        self._step_pool = None                   # the memory pool all step graphs record into, and the stream they record on
-        self._step_stream = None
+        self._step_pool = None                   # the memory pool all step graphs record into
+        self._capture_stream: Optional[torch.cuda.Stream] = None
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -407,6 +407,12 @@ class ModelRunner:
         self._step_graphs[key] = graph
         return graph
 
+    def capture_stream(self) -> torch.cuda.Stream:
+        """The side stream graphs are recorded on (a recording may not run on the default stream)."""
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(self.device)
+        return self._capture_stream
+
     def mark_device_begin(self) -> None:
         if self.timing is not None:
             self._timing_start = torch.cuda.Event(enable_timing=True)
@@ -466,6 +472,35 @@ class ModelRunner:
         self.graph_steps += 1
         self.tokens_run += len(entries)
         return logits[:len(entries)]
+
+
+def record_graph(device: torch.device, forward, stream: torch.cuda.Stream, pool=None):
+    """Record ``forward()`` into a CUDA graph on ``stream`` and return ``(graph, what forward returned)``.
+
+    Done by hand rather than under ``torch.cuda.graph``: that synchronises, collects garbage and empties the allocator's
+    cache on the way in, which made a recording cost as much as twenty steps (0.2 s for a decode graph) and the steps
+    after it pay for fresh device memory.  The cyclic collector is off meanwhile instead: collecting inside a recording
+    could destroy another engine's graph, which is an error there; relaxed mode lets other threads use the allocator.
+    ``pool``: a memory pool shared with graphs that never run at the same time as this one."""
+    graph = torch.cuda.CUDAGraph()
+    stream.wait_stream(torch.cuda.current_stream(device))
+    collecting = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.stream(stream):
+            if pool is not None:
+                graph.capture_begin(pool=pool, capture_error_mode="relaxed")
+            else:
+                graph.capture_begin(capture_error_mode="relaxed")
+            try:
+                result = forward()
+            finally:
+                graph.capture_end()
+    finally:
+        if collecting:
+            gc.enable()
+    torch.cuda.current_stream(device).wait_stream(stream)
+    return graph, result
 
 
 class DecodeGraph:
@@ -628,12 +663,7 @@ class DecodeGraph:
         self._forward()
         self.kernels_per_replay = kernels.launch_count - before
         torch.cuda.synchronize(self.runner.device)
-        # Destroying another graph (an engine dropped earlier, collected just now) is an error inside a capture
-        # in the default mode and would invalidate this one: collect garbage first and capture in relaxed mode.
-        gc.collect()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, capture_error_mode="relaxed"):
-            self.logits = self._forward()
+        self.graph, self.logits = record_graph(self.runner.device, self._forward, self.runner.capture_stream())
         torch.cuda.synchronize(self.runner.device)
 
     def replay(self) -> torch.Tensor:
@@ -698,31 +728,10 @@ class StepGraph:
             return torch.empty((0, runner.vocab_size), dtype=torch.float32, device=runner.device)
 
         logits = forward()                       # this step's result; also creates what must exist before a capture
-        # Recorded by hand rather than under ``torch.cuda.graph``: that empties the allocator's cache and collects
-        # garbage on the way in, which made a capture cost as much as twenty steps and the steps after it pay for fresh
-        # device memory.  All step graphs record into one memory pool: they never run at the same time, so the
-        # intermediates of one may lie where another's do (a graph's result stays allocated, it is not an
-        # intermediate).  The cyclic collector is off meanwhile: it could destroy another engine's graph inside the
-        # recording (see DecodeGraph.capture); relaxed mode lets the allocator work on other threads.
+        # All step graphs record into one memory pool: they never run at the same time, so the intermediates of one may
+        # lie where another's do (a graph's result stays allocated, it is not an intermediate).
         if runner._step_pool is None:
             runner._step_pool = torch.cuda.graph_pool_handle()
-            runner._step_stream = torch.cuda.Stream(runner.device)
-        graph = torch.cuda.CUDAGraph()
-        side = runner._step_stream
-        side.wait_stream(torch.cuda.current_stream(runner.device))
-        collecting = gc.isenabled()
-        gc.disable()
-        try:
-            with torch.cuda.stream(side):
-                graph.capture_begin(pool=runner._step_pool, capture_error_mode="relaxed")
-                try:
-                    self.logits = forward()      # recorded, not run
-                finally:
-                    graph.capture_end()
-        finally:
-            if collecting:
-                gc.enable()
-        torch.cuda.current_stream(runner.device).wait_stream(side)
-        self.graph = graph
+        self.graph, self.logits = record_graph(runner.device, forward, runner.capture_stream(), pool=runner._step_pool)
         runner.step_graph_captures += 1
         return logits[:wanted]
