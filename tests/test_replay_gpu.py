@@ -259,3 +259,50 @@ def test_step_graphs_pad_to_their_bucket_and_do_not_thrash(model_folders, monkey
     # often as it comes, and never pushes one out
     assert len(graphed._step_graphs) == 2 and graphed.step_graph_captures == 2
     assert graphed.step_graph_replays == 2 * 4
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_context_of_eight_thousand_tokens(dtype, tmp_path):
+    """A request of 8 230 tokens — past the third class of context lengths that decode graphs are recorded for, 515 pages
+    in its block table, rotation angles at positions no other test reaches — beside a short one: the prompt in three
+    portions (each starting thousands of keys into the cache), then thirty tokens one by one in a two-row decode graph
+    whose rows hold 8 200 and 60 keys.  bfloat16 on head size 128 (tcgen05 attention with a long prefix, decode through
+    TMA with many splits), 32-bit on the all-sizes kernels; against the plain implementation at the wanted places."""
+    import plain_qwen3
+    import torch
+    from conftest import GAINS, TINY_A, TINY_D, note_error
+    from cuinfer_b200.weights import write_random_model
+
+    base = TINY_D if dtype == "bfloat16" else TINY_A
+    cfg = dict(base, num_hidden_layers=1 if dtype == "bfloat16" else 2, max_position_embeddings=9216)
+    folder = str(tmp_path / "long_model")
+    write_random_model(folder, cfg, 21, std=0.05, gain_std=0.1, dtype=dtype, gains=GAINS[dtype])
+    long_ids = random_tokens(cfg["vocab_size"], 8230, 77)
+    short_ids = random_tokens(cfg["vocab_size"], 90, 78)
+    steps, s = [], 0
+    for lo, hi, want in [(0, 3000, [2999]), (3000, 6000, [0, 1500, 2999]), (6000, 8200, [0, 2199])]:
+        steps.append({"step": s, "entries": [{"id": "long", "tokens": long_ids[lo:hi], "want": want}], "end": []})
+        s += 1
+    steps.append({"step": s, "entries": [{"id": "short", "tokens": short_ids[:60], "want": [59]}], "end": []})
+    s += 1
+    for i in range(30):
+        steps.append({"step": s, "entries": [{"id": "long", "tokens": [long_ids[8200 + i]], "want": [0]},
+                                               {"id": "short", "tokens": [short_ids[60 + i]], "want": [0]}],
+                      "end": ["long", "short"] if i == 29 else []})
+        s += 1
+    out = str(tmp_path / "out")
+    runner = traces.replay_in_process(folder, dtype, steps, out, traces.live_token_peak(steps), 16, cuda_graph=True)
+    assert runner.graph_steps == 30
+    got = traces.collect(steps, out, cfg["vocab_size"])
+    pcfg, weights = plain_qwen3.load_folder(folder)
+    worst = 0.0
+    for rid, ids in (("long", long_ids), ("short", short_ids)):
+        places = sorted(got[rid])
+        ref = plain_qwen3.logits_at(pcfg, weights, ids, places).numpy()
+        scale = float(np.abs(ref).max())
+        for row, place in zip(ref, places):
+            assert np.isfinite(got[rid][place]).all()
+            err = float(np.abs(got[rid][place] - row).max()) / scale
+            worst = max(worst, err)
+            assert err <= TOLERANCE[dtype], f"request {rid}: position {place} is off by {err:.3e} of the largest logit"
+    note_error(dtype, "a context of 8 230 tokens", worst)
