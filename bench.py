@@ -55,9 +55,14 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the measurement runs.
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    nvidia-smi needs a tenth of a second before its first sample and the timed steps of the small shape take less than
+    that together, so the sampler starts before the requests are prefilled (the GPU is under this process's load from
+    then on) and every sample carries its time: ``stop(window)`` reports the samples inside the timed window when
+    there are at least three, else all samples from the prefill on, and says which."""
+
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self) -> None:
@@ -71,9 +76,12 @@ class ClockSampler:
         fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
         os.close(fd)
         self.proc = subprocess.Popen([exe, "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                      "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                                      "-lms", "50"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
 
-    def stop(self) -> dict:
+    def stop(self, window=None) -> dict:
+        """``window``: (start, end) of the timed steps as ``time.time()`` values."""
+        import datetime
+
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -81,24 +89,26 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        clocks, max_clock, reasons = [], None, set()
+        samples, max_clock = [], None
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         with open(self.path) as fh:
             for line in fh:
                 parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 6:
+                if len(parts) < 7:
                     continue
                 try:
-                    clocks.append(float(parts[0]))
-                    max_clock = float(parts[1])
+                    when = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    clock = float(parts[1])
+                    max_clock = float(parts[2])
                 except ValueError:
                     continue
-                for name, val in zip(names, parts[2:6]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
+                samples.append((when, clock, {n for n, v in zip(names, parts[3:7]) if v.lower().startswith("active")}))
         os.remove(self.path)
-        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
-                "reasons": sorted(reasons), "samples": len(clocks)}
+        inside = [x for x in samples if window and window[0] <= x[0] <= window[1]]
+        used, where = (inside, "timed steps") if len(inside) >= 3 else (samples, "prefill, warm-up and timed steps")
+        reasons = set().union(*[x[2] for x in used]) if used else set()
+        return {"sm_mhz": statistics.median(x[1] for x in used) if used else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(used), "window": where}
 
 
 def weight_bytes(cfg: dict, layers: int) -> int:
@@ -152,6 +162,9 @@ def measure_decode(folder: str, batch: int, steps: int, warmup: int, args, sampl
     prompt_len = context - total_steps - prefill_steps - 1
     gen = torch.Generator().manual_seed(1234 + batch)
     params = SamplingParams(temperature=0.0, max_tokens=context - prompt_len, ignore_eos=True)
+    clocks = ClockSampler()
+    if sample_clocks:
+        clocks.start()
     for i in range(batch):
         prompt = torch.randint(0, MODEL["vocab_size"], (prompt_len,), generator=gen).tolist()
         engine.add_request(f"b{i}", prompt, params)
@@ -163,13 +176,11 @@ def measure_decode(folder: str, batch: int, steps: int, warmup: int, args, sampl
     torch.cuda.synchronize()
     ctx_start = statistics.mean(len(r.token_ids) for r in engine.scheduler.requests.values())
     engine.runner.timing = []
-    clocks = ClockSampler()
-    if sample_clocks:
-        clocks.start()
     launches_before = kernels.launch_count
     graph_before = engine.runner.graph_steps
     torch.cuda.synchronize()
     torch.cuda.nvtx.range_push(f"timed_decode_b{batch}")      # lets a profiler pick the timed launches (--nvtx-include)
+    window_start = time.time()
     t0 = time.perf_counter()
     tokens = 0
     for _ in range(steps):
@@ -177,7 +188,7 @@ def measure_decode(folder: str, batch: int, steps: int, warmup: int, args, sampl
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
     torch.cuda.nvtx.range_pop()
-    clock_info = clocks.stop() if sample_clocks else None
+    clock_info = clocks.stop((window_start, time.time())) if sample_clocks else None
     device_ms = sum(a.elapsed_time(b) for a, b in engine.runner.timing)
     pairs = len(engine.runner.timing)
     engine.runner.timing = None
