@@ -32,7 +32,8 @@ def make_runner(model_dir: str, dtype: str, max_tokens: int, block_size: int = 1
     """A runner whose page pool holds exactly ``max_tokens`` tokens (rounded up to whole pages).
     ``cuda_graph``: steps go the way generation sends them — a step of single tokens that all want their logits
     through ``ModelRunner.decode_step`` (one CUDA graph per bucket of rows and class of context length), a
-    prompt-sized step whose shape has been seen before through its captured graph; default: every step eagerly."""
+    step of other shape, padded to a bucket of sizes that has come before, through the graph captured for the
+    bucket; default: every step eagerly."""
     if max_tokens <= 0:
         raise ValueError("--max-tokens must be positive")
     unit = max(TRACE_TOKEN_ROUNDING, block_size)
@@ -89,7 +90,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                         help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     parser.add_argument("--graphs", action="store_true",
-                        help="run decode steps and repeated prompt shapes from CUDA graphs, as generation does")
+                        help="run decode steps and steps whose bucket of sizes has come before from CUDA graphs, as generation does")
     args = parser.parse_args(argv)
     runner = make_runner(args.model, args.dtype, args.max_tokens, args.block_size, cuda_graph=args.graphs)
     run_trace(runner, sys.stdin, args.out)

@@ -172,7 +172,7 @@ def test_decode_graphs_per_context_class(model_folders):
 
 
 def test_repeated_prompt_shapes_replay_a_graph(model_folders):
-    """A prompt-sized step whose shape was seen before is captured and then replayed: four rounds of prompts of the
+    """A prompt-sized step whose bucket of sizes has come before is captured and then replayed: four rounds of prompts of the
     same lengths but other tokens, on other pages of the pool (pages that were given back are taken last), give the
     plain implementation's tokens every time."""
     from cuinfer_b200 import LLM, SamplingParams
