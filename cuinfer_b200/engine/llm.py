@@ -36,6 +36,11 @@ class LLM:
         self.engine = EngineCore(self.config)
         self._counter = 0
 
+    def warm_up(self, batch_sizes: Sequence[int] = (1, 2, 4, 8), longest: int = 2048) -> int:
+        """Record the CUDA graphs of decode steps of these batch sizes, for contexts up to ``longest`` tokens, before
+        the first request needs them.  Returns how many were recorded."""
+        return self.engine.runner.warm_up(batch_sizes, longest)
+
     def _check(self, prompt: Sequence[int], params: SamplingParams) -> None:
         n = len(prompt)
         limit = self.engine.max_model_len

@@ -111,7 +111,7 @@ class ModelRunner:
         self._step_seen: Dict[tuple, int] = {}
         self.step_graph_replays = 0
         self.step_graph_captures = 0
-        self._step_pool = None                   # the memory pool all step graphs record into
+        self._graph_pool = None                  # the memory pool all graphs of this runner record into
         self._capture_stream: Optional[torch.cuda.Stream] = None
         self.steps_run = 0
         self.tokens_run = 0
@@ -407,6 +407,32 @@ class ModelRunner:
         self._step_graphs[key] = graph
         return graph
 
+    def graph_pool(self):
+        """The one memory pool that all graphs of this runner record into.  They never run at the same time, so the
+        intermediates of one may lie where another's do, and the pool grows to the largest graph instead of the sum of
+        all; a graph's result (its logits) stays allocated and is never an intermediate of another.  A result is
+        overwritten by whichever graph runs next, so it is consumed — sampled from, on the same stream — before the
+        next step is launched."""
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
+
+    def warm_up(self, rows: Sequence[int] = (1, 2, 4, 8), longest: int = 2048) -> int:
+        """Record the decode graphs for these numbers of requests and every class of context length up to ``longest``
+        tokens ahead of the first request, instead of when each is first needed (a recording takes 10 to 20 ms, the
+        first one of a process more).  The reference records all its buckets when it starts
+        (csrc/executor/model_runner.cpp:40-52).  Returns how many graphs were recorded."""
+        if not (self.config.enable_cuda_graph and self.model.capturable):
+            return 0
+        before = len(self._graphs)
+        longest = min(longest, self.max_model_len)
+        classes = [c for c in self.GRAPH_CONTEXTS if c < longest] + [longest]
+        for n in rows:
+            if 1 <= n <= min(self.config.max_num_seqs, self.GRAPH_BUCKETS[-1]):
+                for c in classes:
+                    self.decode_graph(n, c)
+        return len(self._graphs) - before
+
     def capture_stream(self) -> torch.cuda.Stream:
         """The side stream graphs are recorded on (a recording may not run on the default stream)."""
         if self._capture_stream is None:
@@ -663,7 +689,8 @@ class DecodeGraph:
         self._forward()
         self.kernels_per_replay = kernels.launch_count - before
         torch.cuda.synchronize(self.runner.device)
-        self.graph, self.logits = record_graph(self.runner.device, self._forward, self.runner.capture_stream())
+        self.graph, self.logits = record_graph(self.runner.device, self._forward, self.runner.capture_stream(),
+                                               pool=self.runner.graph_pool())
         torch.cuda.synchronize(self.runner.device)
 
     def replay(self) -> torch.Tensor:
@@ -728,10 +755,6 @@ class StepGraph:
             return torch.empty((0, runner.vocab_size), dtype=torch.float32, device=runner.device)
 
         logits = forward()                       # this step's result; also creates what must exist before a capture
-        # All step graphs record into one memory pool: they never run at the same time, so the intermediates of one may
-        # lie where another's do (a graph's result stays allocated, it is not an intermediate).
-        if runner._step_pool is None:
-            runner._step_pool = torch.cuda.graph_pool_handle()
-        self.graph, self.logits = record_graph(runner.device, forward, runner.capture_stream(), pool=runner._step_pool)
+        self.graph, self.logits = record_graph(runner.device, forward, runner.capture_stream(), pool=runner.graph_pool())
         runner.step_graph_captures += 1
         return logits[:wanted]

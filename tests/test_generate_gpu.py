@@ -404,3 +404,23 @@ def test_weights_drawn_on_the_device_equal_the_host_generator(tmp_path, stored, 
     prompts = [random_tokens(TINY_B["vocab_size"], n, 950 + i) for i, n in enumerate([11, 40])]
     p = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
     assert [r.token_ids for r in a.generate(prompts, p)] == [r.token_ids for r in b.generate(prompts, p)]
+
+
+def test_warm_up_records_the_decode_graphs_ahead(model_folders):
+    """After ``warm_up`` the first decode steps find their graphs recorded: generation adds none, and gives the plain
+    implementation's tokens."""
+    from cuinfer_b200 import LLM, SamplingParams
+
+    folders, cfg, block = model_folders["B"]
+    pcfg, weights = plain_qwen3.load_folder(folders["float32"])
+    llm = LLM(folders["float32"], dtype="float32", block_size=block, num_blocks=64, max_num_seqs=4)
+    recorded = llm.warm_up(batch_sizes=(1, 2, 3), longest=600)
+    runner = llm.engine.runner
+    assert recorded == len(runner._graphs) == 3 * 2        # rows 1, 2 and 4 (for 3), context classes 512 and 600
+    assert llm.warm_up(batch_sizes=(1, 2, 3), longest=600) == 0
+    prompts = [random_tokens(cfg["vocab_size"], n, 640 + i) for i, n in enumerate([40, 33, 21])]
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    for prompt, res in zip(prompts, out):
+        assert res.token_ids == plain_qwen3.greedy_generate(pcfg, weights, prompt, 6)
+    assert len(runner._graphs) == 6 and runner.graph_steps > 0
+    runner.manager.check()
