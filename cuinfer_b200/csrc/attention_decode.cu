@@ -550,8 +550,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     bool cluster = tma && cluster_combine_fits(splits, g, D);
     if (cluster) {
         const size_t with_inbox = smem + cluster_inbox_bytes(splits, g, D);
-        const int resident = tma ? max_resident_clusters(paged_attention_decode_kernel<D, true, true>, splits, with_inbox)
-                                 : max_resident_clusters(paged_attention_decode_kernel<D, false, true>, splits, with_inbox);
+        const int resident = max_resident_clusters(paged_attention_decode_kernel<D, true, true>, splits, with_inbox);
         cluster = resident >= nkv * num_requests;
         if (cluster) smem = with_inbox;
     }
@@ -566,10 +565,22 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                                   nkv, scale_log2, window, splits, part_o, part_ml, counters, kv_map, error_flag, warm,
                                   warm_bytes, inbox_offset);
     };
-    static SmemLimit limits[4];          // one per instantiation of this head size
-    cudaError_t e;
-    if (tma) e = cluster ? launch(paged_attention_decode_kernel<D, true, true>, limits[0]) : launch(paged_attention_decode_kernel<D, true, false>, limits[1]);
-    else e = cluster ? launch(paged_attention_decode_kernel<D, false, true>, limits[2]) : launch(paged_attention_decode_kernel<D, false, false>, limits[3]);
+    static SmemLimit limits[3];          // one per instantiation of this head size
+    cudaError_t e = cudaSuccess;
+    if (cluster) {
+        // should the cluster launch be refused after all (the occupancy query is a forecast), the step is not lost:
+        // the same work runs without clusters, combined through the scratch
+        e = launch(paged_attention_decode_kernel<D, true, true>, limits[0]);
+        if (e != cudaSuccess && e != cudaErrorUnknown) {
+            (void)cudaGetLastError();
+            cluster = false;
+            smem -= cluster_inbox_bytes(splits, g, D);
+        }
+    }
+    if (!cluster) {
+        e = tma ? launch(paged_attention_decode_kernel<D, true, false>, limits[1])
+                : launch(paged_attention_decode_kernel<D, false, false>, limits[2]);
+    }
     if (e == cudaErrorUnknown) return -2;          // the message is set
     if (e != cudaSuccess) {
         set_error("paged_attention_decode: launch failed: %s", cudaGetErrorString(e));
