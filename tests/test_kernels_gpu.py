@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import random
 
 import pytest
 import torch
@@ -507,6 +508,33 @@ def test_attention_tcgen05(nq, nkv, ps, window):
     close(out, attention_reference(case, lens, new, scale, window), 1.5e-2)
     assert not k.attention_tcgen05_supports(64, 8, 8, 16) and not k.attention_tcgen05_supports(128, 12, 4, 16)
     assert not k.attention_tcgen05_supports(128, 8, 8, 5) and not k.attention_tcgen05_supports(128, 8, 8, 4)
+
+
+@pytest.mark.parametrize("requests", [3, 45])
+@pytest.mark.parametrize("splits", [2, 4])
+def test_paged_attention_decode_cluster_and_memory_combine(requests, splits):
+    """Two to four splits on the TMA path meet in a cluster's shared memory while all clusters of the launch run at
+    once (3 requests x 8 heads), and through the scratch buffer when they would not (45 x 8 clusters): both against the
+    plain attention, and the copy paths against each other."""
+    k = _k()
+    nq, nkv, d, ps = 16, 8, 128, 16
+    rnd = random.Random(requests * 10 + splits)
+    lens = [rnd.choice([1, 30, 64, 65, 200, 500, 1100]) for _ in range(requests)]
+    new = [1] * requests
+    case = attention_case(torch.bfloat16, nq, nkv, d, lens, new, ps, seed=90 + splits, sharp=True, poison=True)
+    scale = 1.0 / math.sqrt(d)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    cache, bt, wide = case["cache"].to(DEV), case["bt"].to(DEV), case["wide"].to(DEV)
+    want = attention_reference(case, lens, new, scale)
+    outs = []
+    for tma in (True, False, True):
+        out = torch.full((requests, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+        k.paged_attention_decode(wide, out, cache, bt, sl, nq, nkv, d, scale, 0, splits, tma=tma)
+        k.check_error_flags()
+        close(out, want, 1.5e-2)
+        outs.append(out)
+    close(outs[0], outs[1], 1e-2)
+    assert torch.equal(outs[0], outs[2])
 
 
 def test_paged_attention_decode_refuses_other_sizes():
