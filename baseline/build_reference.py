@@ -86,7 +86,7 @@ def build(source: str | None = None, jobs: int = 0, force: bool = False) -> str:
     """Returns the path of the binary; raises RuntimeError with the compiler's message when something fails."""
     csrc = os.path.join(REF, "csrc")
     if not os.path.isdir(csrc):
-        source = source or os.environ.get("CUINFER_REFERENCE_SOURCE", "/root/reference")
+        source = source or os.environ.get("CUINFER_REFERENCE_SOURCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
         if not os.path.isdir(os.path.join(source, "csrc")):
             raise RuntimeError(f"the reference's sources are not at {source} and no copy is under baseline/_ref/csrc")
         os.makedirs(REF, exist_ok=True)

@@ -1,6 +1,7 @@
 """The scheduler and the cache manager against the reference's own, step by step, on the CPU.
 
-When a checkout of the reference is at hand (``$CUINFER_REFERENCE_SOURCE``, default ``/root/reference``), its
+When a checkout of the reference is at hand (``$CUINFER_REFERENCE_SOURCE``, default: a folder ``reference`` beside
+this repository), its
 ``csrc/scheduler/scheduler.cpp`` and ``csrc/scheduler/kv_cache_manager.cpp`` are compiled unchanged, in a temporary
 folder, with a small driver (``tests/differential/reference_scheduler_driver.cpp``), ``nlohmann/json.hpp`` from an
 installed package and a two-macro stand-in for ``msgpack.hpp``; nothing is copied into this repository.  The same
@@ -25,7 +26,8 @@ from cuinfer_b200.engine.scheduler import FinishReason, Scheduler
 from cuinfer_b200.sampling import SamplingParams
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE = os.environ.get("CUINFER_REFERENCE_SOURCE", "/root/reference")
+REFERENCE = os.environ.get("CUINFER_REFERENCE_SOURCE",
+                           os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 MSGPACK_STUB = "#pragma once\n#define MSGPACK_DEFINE_MAP(...)\n#define MSGPACK_ADD_ENUM(...)\n"
 
