@@ -291,7 +291,14 @@ def decode_uses_tma(max_seq_len: int, splits: int) -> bool:
     return -(-max_seq_len // splits) >= DECODE_TMA_MIN_KEYS
 
 
-def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots: int = 296, tma: bool = False) -> int:
+def decode_slots(head_dim: int) -> int:
+    """CTAs of the decode attention kernel that the GPU runs at a time: its key and value rings take 768 bytes per
+    value of the head size, so one CTA per SM at head size 256, two at 128, and three (by registers) below."""
+    return 148 * (1 if head_dim > 128 else 2 if head_dim > 64 else 3)
+
+
+def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots: int = 296, tma: bool = False,
+                  head_dim: int = 128) -> int:
     """How many CTAs share the keys of one (request, kv head).  ``tma``: the cache layout allows the TMA path, which
     a split then takes if it leaves a CTA ``DECODE_TMA_MIN_KEYS`` keys or more.
 
@@ -301,19 +308,21 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, slots:
     memory's pace when n CTAs stream at once) plus a fixed cost for a CTA's start and its partial results; splitting
     adds 3000 for the combine and 40 per split.  A CTA's own pace is 16 per key and 3000 fixed on the TMA path, 18 and
     4000 on the cp.async path.  The constants were fitted to timings at batch 1 to 128 with 300 to 9000 keys of head
-    size 128 (largest miss 1.7 us, 9 % r.m.s. error of the estimate).  The smallest estimate wins.
+    size 128 (largest miss 1.7 us, 9 % r.m.s. error of the estimate); for another head size the costs per key scale
+    with the bytes of a key.  The smallest estimate wins.
     """
     pairs = max(1, num_requests * num_kv_heads)
+    width = head_dim / 128.0
     best, best_cost = 1, None
     for s in range(1, 65):
         keys = -(-(-(-max_seq_len // s)) // 64) * 64
         if s > 1 and (s - 1) * keys >= max_seq_len:
             continue                                   # the last CTA would get nothing: a smaller s does the same
-        per_key, fixed = (16.0, 3000.0) if tma and decode_uses_tma(max_seq_len, s) else (18.0, 4000.0)
+        per_key, fixed = (16.0 * width, 3000.0) if tma and decode_uses_tma(max_seq_len, s) else (18.0 * width, 4000.0)
         full, rest = divmod(pairs * s, slots)
-        cost = full * (keys * max(per_key, 0.072 * slots) + fixed)
+        cost = full * (keys * max(per_key, 0.072 * width * slots) + fixed)
         if rest:
-            cost += keys * max(per_key, 0.072 * rest) + fixed
+            cost += keys * max(per_key, 0.072 * width * rest) + fixed
         if s > 1:
             cost += 3000.0 + 40.0 * s
         if best_cost is None or cost < best_cost:

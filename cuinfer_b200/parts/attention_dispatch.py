@@ -28,7 +28,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: Step
             and kernels.paged_attention_decode_supports(head_dim, num_heads, num_kv_heads)):
         longest = max(1, ctx.max_seq_len)
         tma = kernels.decode_tma_takes(kv.group.page_size, head_dim, window)
-        splits = kernels.decode_splits(ctx.num_requests, num_kv_heads, longest, tma=tma)
+        splits = kernels.decode_splits(ctx.num_requests, num_kv_heads, longest, kernels.decode_slots(head_dim), tma=tma,
+                                       head_dim=head_dim)
         tma = tma and kernels.decode_uses_tma(longest, splits)
         kernels.paged_attention_decode(qkv, out, kv.cache, kv.group.block_table, ctx.seq_lens, num_heads,
                                        num_kv_heads, head_dim, scale, window, splits, tma=tma, warm=warm)
