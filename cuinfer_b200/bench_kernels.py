@@ -60,30 +60,31 @@ def attention_decode(args) -> dict:
 
 
 def attention_prefill(args) -> dict:
-    """One request of ``--tokens`` new tokens after ``--prefix`` cached ones."""
+    """``--requests`` requests of ``--tokens`` new tokens each after ``--prefix`` cached ones, in one launch."""
     n, prefix, nq, nkv, d, ps = args.tokens, args.prefix, args.q_heads, args.kv_heads, args.head_dim, args.page_size
+    R = max(1, args.requests)
     total = n + prefix
     pages = (total + ps - 1) // ps
     dev = "cuda:0"
-    cache = torch.randn(pages, 2, nkv, ps, d, device=dev, dtype=torch.bfloat16)
-    table = torch.randperm(pages, device=dev).to(torch.int32).view(1, pages)
-    q = torch.randn(n, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16)
-    out = torch.empty(n, nq * d, device=dev, dtype=torch.bfloat16)
-    qsl = torch.tensor([0, n], dtype=torch.int32, device=dev)
-    sl = torch.tensor([total], dtype=torch.int32, device=dev)
+    cache = torch.randn(R * pages, 2, nkv, ps, d, device=dev, dtype=torch.bfloat16)
+    table = torch.randperm(R * pages, device=dev).to(torch.int32).view(R, pages)
+    q = torch.randn(R * n, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(R * n, nq * d, device=dev, dtype=torch.bfloat16)
+    qsl = torch.arange(R + 1, dtype=torch.int32, device=dev) * n
+    sl = torch.full((R,), total, dtype=torch.int32, device=dev)
     scale = 1.0 / math.sqrt(d)
 
     def run(i):
         if args.impl == "tcgen05":
-            kernels.attention_tcgen05(q, out, cache, table, qsl, sl, [n], nq, nkv, d, scale, 0)
+            kernels.attention_tcgen05(q, out, cache, table, qsl, sl, [n] * R, nq, nkv, d, scale, 0)
         else:
-            kernels.paged_attention_prefill(q, out, cache, table, qsl, sl, [n], nq, nkv, d, scale, 0)
+            kernels.paged_attention_prefill(q, out, cache, table, qsl, sl, [n] * R, nq, nkv, d, scale, 0)
 
     ms = _time(run, args.iters)
     if args.impl == "tcgen05":
         kernels.check_error_flags()
-    flops = 4.0 * nq * d * (n * prefix + n * (n + 1) / 2.0)
-    return {"kernel": f"attention_prefill[{args.impl}]", "tokens": n, "prefix": prefix, "ms": round(ms, 4),
+    flops = R * 4.0 * nq * d * (n * prefix + n * (n + 1) / 2.0)
+    return {"kernel": f"attention_prefill[{args.impl}]", "requests": R, "tokens": n, "prefix": prefix, "ms": round(ms, 4),
             "TFLOPs": round(flops / ms / 1e9, 1)}
 
 
@@ -178,6 +179,7 @@ def main(argv=None) -> int:
     f = sub.add_parser("attention_prefill")
     f.add_argument("--tokens", type=int, default=2048)
     f.add_argument("--prefix", type=int, default=0)
+    f.add_argument("--requests", type=int, default=1)
     f.add_argument("--q-heads", type=int, default=16)
     f.add_argument("--kv-heads", type=int, default=8)
     f.add_argument("--head-dim", type=int, default=128)

@@ -101,24 +101,44 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
     const int kvh = blockIdx.x;     // heads vary fastest: every head's longest tile starts before any shorter one
     const int g = nq / nkv;
 
-    if (tid == 0) {
-        int t = gridDim.y - 1 - blockIdx.y, r = 0;      // later (longer) tiles first
-        for (; r < num_requests; ++r) {
-            const int tiles = ((query_start_loc[r + 1] - query_start_loc[r]) * g + kM - 1) / kM;
-            if (t < tiles) break;
-            t -= tiles;
+    const int g_shift = 31 - __clz(g);      // g divides 128: a power of two
+
+    if (warp == 0) {
+        // which request and which of its row tiles: the whole warp looks, 32 requests at a time (one thread walking up
+        // to 64 requests took 6 us, and nothing else of the tile can start before this is known)
+        int t = gridDim.y - 1 - blockIdx.y;     // later (longer) tiles first
+        int req = num_requests, tile = 0;
+        for (int r0 = 0; r0 < num_requests; r0 += 32) {
+            const int r = r0 + lane;
+            int tiles = 0;
+            if (r < num_requests) tiles = ((query_start_loc[r + 1] - query_start_loc[r]) * g + kM - 1) / kM;
+            int upto = tiles;                   // tiles of the requests r0 .. r
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, upto, d);
+                if (lane >= d) upto += o;
+            }
+            const unsigned hit = __ballot_sync(0xffffffffu, r < num_requests && t < upto);
+            if (hit) {
+                const int first = __ffs(hit) - 1;
+                req = r0 + first;
+                tile = t - (__shfl_sync(0xffffffffu, upto, first) - __shfl_sync(0xffffffffu, tiles, first));
+                break;
+            }
+            t -= __shfl_sync(0xffffffffu, upto, 31);
         }
-        s_req = r; s_tile = t; s_abort = 0;
-        if (r < num_requests) {     // read here once, so that the other threads need no round trip of their own after the barrier
-            s_q0 = query_start_loc[r];
-            s_n = query_start_loc[r + 1] - query_start_loc[r];
-            s_seq = seq_lens[r];
+        if (lane == 0) {
+            s_req = req; s_tile = tile; s_abort = 0;
+            if (req < num_requests) {   // read here once, so that the other threads need no round trip of their own after the barrier
+                s_q0 = query_start_loc[req];
+                s_n = query_start_loc[req + 1] - query_start_loc[req];
+                s_seq = seq_lens[req];
+            }
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
         }
-        for (int i = 0; i < kKBufs; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_free[i], 1); }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&v_full[i], 1); mbar_init(&v_free[i], 1); mbar_init(&s_full[i], 1);
-            mbar_init(&p_ready[i], 8); mbar_init(&pv_done[i], 1);
-        }
+    } else if (warp == 1 && lane < 16) {
+        // a thread per barrier: p_ready (at 7 and 8) counts the eight warps of a softmax group, all others one arrival
+        mbar_init(&bars[lane], lane == 7 || lane == 8 ? 8 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -147,22 +167,32 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
         rows_total = n * g;
         row0 = s_tile * kM;
         const int last_row = min(row0 + kM, rows_total) - 1;
-        const int pos_first = seq_len - n + row0 / g, pos_last = seq_len - n + last_row / g;
+        const int pos_first = seq_len - n + (row0 >> g_shift), pos_last = seq_len - n + (last_row >> g_shift);
         k_lo = window > 0 ? max(0, pos_first - window + 1) / kN * kN : 0;
         num_tiles = (pos_last + 1 - k_lo + kN - 1) / kN;
     }
 
     if (active && warp < kMmaWarp) {
         // ---- the query tile: row = token_local * g + head_in_group, two swizzled 64-column panels ----
-        for (int idx = tid; idx < kM * 16; idx += kMmaWarp * 32) {
+        // (a thread's four loads are all on their way before the first is stored: one round trip, not four)
+        constexpr int kPer = kM * 16 / (kMmaWarp * 32);
+        uint4 v[kPer];
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int idx = tid + u * kMmaWarp * 32;
             const int row = idx >> 4, c = idx & 15;
             const int grow = row0 + row;
-            uint4 v = make_uint4(0, 0, 0, 0);
+            v[u] = make_uint4(0, 0, 0, 0);
             if (grow < rows_total) {
-                const int tl = grow / g, hi = grow % g;
-                v = *reinterpret_cast<const uint4*>(q + (size_t)(q0 + tl) * q_stride + (size_t)(kvh * g + hi) * kD + c * 8);
+                const int tl = grow >> g_shift, hi = grow & (g - 1);
+                v[u] = *reinterpret_cast<const uint4*>(q + (size_t)(q0 + tl) * q_stride + (size_t)(kvh * g + hi) * kD + c * 8);
             }
-            *reinterpret_cast<uint4*>(sQ + (c >> 3) * kPanel + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
+        }
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int idx = tid + u * kMmaWarp * 32;
+            const int row = idx >> 4, c = idx & 15;
+            *reinterpret_cast<uint4*>(sQ + (c >> 3) * kPanel + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v[u];
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -298,7 +328,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
         const int row_local = quarter * 32 + lane;
         const int grow = row0 + row_local;
         const bool row_ok = grow < rows_total;
-        const int pos = row_ok ? seq_len - n + grow / g : -1;
+        const int pos = row_ok ? seq_len - n + (grow >> g_shift) : -1;
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         const uint32_t s_col = (uint32_t)(grp * kN), o_col = (uint32_t)(2 * kN + grp * kN);
         auto pair_barrier = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + grp * 4 + quarter) : "memory"); };
@@ -403,30 +433,46 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             const float m = fmaxf(m0, m1);
             const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - m);
             const float total = l0 * w0 + l1 * w1;
-            const float inv = total > 0.f ? 1.f / total : 0.f;
+            // (total is at least 2^-8 for a row with a visible key and at most a few thousand)
+            const float inv = total > 0.f ? __fdividef(1.f, total) : 0.f;
             const float f0 = w0 * inv, f1 = w1 * inv;
             const bool has1 = num_tiles > 1;        // group 1 has an accumulator only if there was a second tile
             uint32_t a[32], b[32];
             tmem_ld_32x32b_x32(lane_addr + (uint32_t)(2 * kN + cb + grp * 32), a);
             if (has1) tmem_ld_32x32b_x32(lane_addr + (uint32_t)(3 * kN + cb + grp * 32), b);
             tmem_ld_wait();
-            if (row_ok) {
-                const int tl = grow / g, hh = grow % g;
-                __nv_bfloat16* dst = out + (size_t)(q0 + tl) * out_stride + (size_t)(kvh * g + hh) * kD + cb + grp * 32;
+            // into the query tile's shared memory (every S has read it), a row's 256 bytes together, its 16-byte pieces
+            // swapped by the row number so that neither these stores nor the loads below meet in a bank
 #pragma unroll
-                for (int e = 0; e < 32; e += 8) {
-                    float y[8];
+            for (int e = 0; e < 32; e += 8) {
+                float y[8];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        y[u] = __uint_as_float(a[e + u]) * f0;
-                        if (has1) y[u] = fmaf(__uint_as_float(b[e + u]), f1, y[u]);
-                    }
-                    uint4 pk;
-                    __nv_bfloat162 t0 = __floats2bfloat162_rn(y[0], y[1]), t1 = __floats2bfloat162_rn(y[2], y[3]);
-                    __nv_bfloat162 t2 = __floats2bfloat162_rn(y[4], y[5]), t3 = __floats2bfloat162_rn(y[6], y[7]);
-                    pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
-                    pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
-                    *reinterpret_cast<uint4*>(dst + e) = pk;
+                for (int u = 0; u < 8; ++u) {
+                    y[u] = __uint_as_float(a[e + u]) * f0;
+                    if (has1) y[u] = fmaf(__uint_as_float(b[e + u]), f1, y[u]);
+                }
+                uint4 pk;
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(y[0], y[1]), t1 = __floats2bfloat162_rn(y[2], y[3]);
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(y[4], y[5]), t3 = __floats2bfloat162_rn(y[6], y[7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
+                pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
+                const int piece = (cb + grp * 32 + e) >> 3;
+                *reinterpret_cast<uint4*>(sQ + row_local * 256 + ((piece ^ (row_local & 15)) << 4)) = pk;
+            }
+        }
+        // out to global memory sixteen threads to a row: a thread that stored its own row's pieces sent 32 partial
+        // sectors with every instruction, and the tile's 2 048 of them took 1.5 us
+        asm volatile("bar.sync 9, %0;" ::"r"(kMmaWarp * 32) : "memory");
+        if (!(*(volatile int*)&s_abort) && num_tiles > 0) {
+#pragma unroll
+            for (int u = 0; u < kM * 16 / (kMmaWarp * 32); ++u) {
+                const int idx = tid + u * kMmaWarp * 32;
+                const int row = idx >> 4, c = idx & 15;
+                const int grow_out = row0 + row;
+                if (grow_out < rows_total) {
+                    const uint4 pk = *reinterpret_cast<const uint4*>(sQ + row * 256 + ((c ^ (row & 15)) << 4));
+                    const int tl = grow_out >> g_shift, hh = grow_out & (g - 1);
+                    *reinterpret_cast<uint4*>(out + (size_t)(q0 + tl) * out_stride + (size_t)(kvh * g + hh) * kD + c * 8) = pk;
                 }
             }
         }
