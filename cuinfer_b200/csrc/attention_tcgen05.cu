@@ -89,8 +89,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
     uint64_t* s_full = bars + 5;       // [2] S of a tile is in tensor memory
     uint64_t* p_ready = bars + 7;      // [2] P of a tile is in tensor memory (8 warps arrive)
     uint64_t* pv_done = bars + 9;      // [2] the group's O includes a tile
-    uint64_t* k_free = bars + 11;      // [kKBufs <= 3] S has read a key buffer (early: its next keys can be fetched)
-    uint64_t* v_free = bars + 14;      // [2] P V has read a value buffer
+    // With two key and two value buffers, tile j's buffers are free again exactly when s_full[j % 2] (S has read the
+    // keys) and pv_done[j % 2] (P V has read the values) complete: the producers wait on those, and the thread that
+    // issues the MMAs, which every tile waits for in turn, has two commits fewer per tile to issue.
+    static_assert(kKBufs == 2 && kVBufs == 2, "the producers take s_full and pv_done for the buffers' release");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     __shared__ int s_req, s_tile, s_abort, s_q0, s_n, s_seq;
     __shared__ float s_mx[2][2][2][128];   // [group][tile parity within the group][column half][row]: the halves' maxima
@@ -213,8 +215,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                 const uint64_t off = (uint64_t)(((k >> 2) * kPanel + (k & 3) * 32) >> 4);
                 umma_bf16(tmem + (uint32_t)(b * kN), qd + off, kd + off, idesc(false), k != 0);
             }
-            umma_commit(&s_full[b]);
-            umma_commit(&k_free[j % kKBufs]);    // the key buffer can be refilled as soon as S has been computed
+            umma_commit(&s_full[b]);            // also: the key buffer can be refilled
         };
         auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
             bool ok = mbar_wait(bar, parity);
@@ -261,8 +262,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                     const uint64_t vd = desc_mnmajor(sV + b * kTileBytes + k * 16 * 128, kPanel);
                     mma_ts(tmem + (uint32_t)(2 * kN + b * kN), tmem + (uint32_t)(b * kN + k * 8), vd, idesc(true), (j >= 2) || k != 0);
                 }
-                umma_commit(&pv_done[b]);
-                umma_commit(&v_free[b]);         // the value buffer can be refilled
+                umma_commit(&pv_done[b]);        // also: the value buffer can be refilled
             }
             __syncwarp();
         }
@@ -305,7 +305,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             if (!ok && lane == 0) { atomicExch(error_flag, code); s_abort = 1; }
             return __all_sync(0xffffffffu, ok);
         };
-        uint64_t* free_bar = kv ? v_free : k_free;
+        uint64_t* free_bar = kv ? pv_done : s_full;
         for (int t = 0; t < depth && t < num_tiles; ++t) {
             lookup(t);
             fill(t);
