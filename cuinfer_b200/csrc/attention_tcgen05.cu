@@ -13,15 +13,17 @@
 //   * S = Q K^T and O += P V are `tcgen05.mma.cta_group::1.kind::f16` with accumulators in tensor memory; K is a
 //     K-major operand, V an MN-major one, straight from the page layout; P is the A operand of P V straight from tensor
 //     memory (bfloat16, written with `tcgen05.st` over the scores it was made from), so it never touches shared memory;
-//   * key tiles alternate between two softmax groups of eight warps, each with its own S, running maximum, running sum
-//     and O in tensor memory (4 x 128 columns), merged at the end like the splits of a split-key kernel: while one group
-//     waits for its scores or its P V, the other computes exponentials.  Inside a group two threads share a row (TMEM
-//     lane = row, 64 columns each): they read S with one `tcgen05.ld` pass, keep the running maximum in base 2 and raise
-//     it only when it grows by more than 8 (so O is rescaled rarely, with `tcgen05.ld`/`tcgen05.st`);
-//   * a seventeenth warp's first lane issues the MMAs; S of tile j+1 is computed while the softmax of tile j runs.
+//   * key tiles alternate between two sets of S, running maximum, running sum and O in tensor memory (4 x 128 columns),
+//     merged at the end like the splits of a split-key kernel: S of tile j+1 is computed and P V of tile j-1 runs while
+//     the sixteen softmax warps take the exponentials of tile j.  Four threads share a row (TMEM lane = row, 32 columns
+//     each): they read S with one `tcgen05.ld`, keep the running maximum in base 2 and raise it only when it grows by
+//     more than 8 (so O is rescaled rarely, with `tcgen05.ld`/`tcgen05.st`);
+//   * a seventeenth warp's first lane issues the MMAs.
 //
 // Every mbarrier wait is bounded; on a time-out the kernel raises the error flag, stops, frees its tensor memory
 // and returns.
+#include <type_traits>
+
 #include "common.cuh"
 #include "mma_utils.cuh"
 #include "tcgen05_utils.cuh"
@@ -54,6 +56,14 @@ __device__ __forceinline__ void tst32(uint32_t taddr, const uint32_t (&r)[32]) {
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tst16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tst_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // shared memory: Q | K0 | K1 | V0 | V1, each 128 rows x 128 columns bf16 = 32 KB as two 64-column panels.  (A third key
@@ -62,7 +72,7 @@ constexpr int kTileBytes = 2 * kPanel;
 constexpr int kKBufs = 2, kVBufs = 2;
 constexpr int kSmemBytes = (1 + kKBufs + kVBufs) * kTileBytes + 1024 + 256;
 
-constexpr int kMmaWarp = 16;                       // warps 0-15: two softmax groups of eight
+constexpr int kMmaWarp = 16;                       // warps 0-15: the softmax
 constexpr int kThreads = (kMmaWarp + 3) * 32;      // + the MMA warp, a producer warp for keys and one for values
 
 // A operand from tensor memory (P, bfloat16, two keys to a column), B from shared memory
@@ -83,21 +93,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
     unsigned char* sK = base + kTileBytes;                      // kKBufs buffers: tile j in buffer j % kKBufs
     unsigned char* sV = base + (1 + kKBufs) * kTileBytes;       // kVBufs buffers
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + (1 + kKBufs + kVBufs) * kTileBytes);
-    // one barrier per buffer; key tile j uses value buffer, tensor-memory half and softmax group j % 2
+    // one barrier per buffer; key tile j uses key and value buffer and tensor-memory set j % 2
     uint64_t* k_full = bars;           // [kKBufs <= 3] a key tile has landed (bytes counted)
     uint64_t* v_full = bars + 3;       // [2] a value tile has landed
     uint64_t* s_full = bars + 5;       // [2] S of a tile is in tensor memory
-    uint64_t* p_ready = bars + 7;      // [2] P of a tile is in tensor memory (8 warps arrive)
-    uint64_t* pv_done = bars + 9;      // [2] the group's O includes a tile
+    uint64_t* p_ready = bars + 7;      // [2] P of a tile is in tensor memory (16 warps arrive)
+    uint64_t* pv_done = bars + 9;      // [2] the set's O includes a tile
     // With two key and two value buffers, tile j's buffers are free again exactly when s_full[j % 2] (S has read the
     // keys) and pv_done[j % 2] (P V has read the values) complete: the producers wait on those, and the thread that
     // issues the MMAs, which every tile waits for in turn, has two commits fewer per tile to issue.
     static_assert(kKBufs == 2 && kVBufs == 2, "the producers take s_full and pv_done for the buffers' release");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     __shared__ int s_req, s_tile, s_abort, s_q0, s_n, s_seq;
-    __shared__ float s_mx[2][2][2][128];   // [group][tile parity within the group][column half][row]: the halves' maxima
-    __shared__ float s_l[2][2][128];       // [group][column half][row]: the halves' sums at the end
-    __shared__ float s_m[2][128];          // [group][row]: the group's reference maximum at the end
+    __shared__ float s_mx[2][4][128];      // [tile parity][column quarter][row]: the quarters' maxima
+    __shared__ float s_l[2][4][128];       // [tile parity][column quarter][row]: the quarters' sums at the end
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.x;     // heads vary fastest: every head's longest tile starts before any shorter one
@@ -139,8 +148,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
         }
     } else if (warp == 1 && lane < 16) {
-        // a thread per barrier: p_ready (at 7 and 8) counts the eight warps of a softmax group, all others one arrival
-        mbar_init(&bars[lane], lane == 7 || lane == 8 ? 8 : 1);
+        // a thread per barrier: p_ready (at 7 and 8) counts the sixteen softmax warps, all others one arrival
+        mbar_init(&bars[lane], lane == 7 || lane == 8 ? kMmaWarp : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -202,8 +211,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
     // way while the queries are still being copied
     if (warp <= kMmaWarp) asm volatile("bar.sync 10, %0;" ::"r"((kMmaWarp + 1) * 32) : "memory");
 
-    // tensor memory: S of group 0 | S of group 1 | O of group 0 | O of group 1, 128 columns each; P of a group (bfloat16,
-    // two keys to a column) takes the first 64 columns of the group's S once the softmax holds S in registers
+    // tensor memory: S of set 0 | S of set 1 | O of set 0 | O of set 1, 128 columns each; P of a set (bfloat16,
+    // two keys to a column) takes the first 64 columns of the set's S once the softmax holds S in registers
     if (active && warp == kMmaWarp) {
         // ---- the MMAs: the whole warp walks the loop, lane 0 issues ----
         auto issue_s = [&](int j) {
@@ -229,7 +238,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             const int b = j & 1;
             const uint32_t parity = (j >> 1) & 1;
             if (j + 1 < num_tiles) {
-                // S(j+1) overwrites S and P of tile j-1 (same group): P V(j-1) was issued before, and the tensor pipe
+                // S(j+1) overwrites S and P of tile j-1 (same set): P V(j-1) was issued before, and the tensor pipe
                 // runs what one thread issues in order
                 ok = wait_all(&k_full[(j + 1) % kKBufs], ((j + 1) / kKBufs) & 1, 12);
                 if (!ok) break;
@@ -317,55 +326,56 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             lookup(j + depth + 1);
         }
     } else if (active && warp < kMmaWarp) {
-        // ---- softmax: group grp (warps 8 grp .. 8 grp + 7) takes the key tiles j = grp, grp + 2, ... with a running
-        // maximum, a running sum and an output accumulator of its own, so that one group's exponentials run while the
-        // other waits for its scores or its P V; the two are merged at the end.  Two threads per row (TMEM lane), each
-        // takes 64 of the 128 columns; warps w and w + 4 of a group share the lanes 32 * (w % 4) .. + 31 and meet at a
-        // named barrier to combine a row's maxima. ----
-        const int grp = warp >> 3;
-        const int quarter = warp & 3, half = (warp >> 2) & 1;
-        const int cb = half * 64;
+        // ---- softmax: all sixteen warps take every key tile, four threads to a row (TMEM lane) with 32 of the 128
+        // columns each; warps w, w + 4, w + 8 and w + 12 share the lanes 32 * (w % 4) .. + 31 and meet at a named barrier
+        // to combine a row's maxima.  Tiles alternate between two sets of scores, running maximum, running sum and
+        // output accumulator (set j % 2), so that the scores of tile j + 1 are computed and the P V of tile j - 1 runs
+        // while the exponentials of tile j are taken; the two sets are merged at the end. ----
+        const int quarter = warp & 3, cq = warp >> 2;
+        const int cb = cq * 32;
         const int row_local = quarter * 32 + lane;
         const int grow = row0 + row_local;
         const bool row_ok = grow < rows_total;
         const int pos = row_ok ? seq_len - n + (grow >> g_shift) : -1;
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t s_col = (uint32_t)(grp * kN), o_col = (uint32_t)(2 * kN + grp * kN);
-        auto pair_barrier = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + grp * 4 + quarter) : "memory"); };
-        float m_used = -INFINITY, l = 0.f;
+        auto row_barrier = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory"); };
+        float m_set[2] = {-INFINITY, -INFINITY}, l_set[2] = {0.f, 0.f};     // indexed by constants only
         bool ok = true;
-        int done = 0;                               // tiles this group has finished
-        for (int j = grp; j < num_tiles; j += 2, ++done) {
-            const uint32_t parity = (uint32_t)(done & 1);
+        // one key tile of set B (a constant after inlining); false if a wait ran out
+        auto softmax_tile = [&](int j, auto set) -> bool {
+            constexpr int B = decltype(set)::value;
+            float& m_used = m_set[B];
+            float& l = l_set[B];
+            const uint32_t s_col = (uint32_t)(B * kN), o_col = (uint32_t)(2 * kN + B * kN);
+            const int done = j >> 1;                    // tiles of this set before this one
             const int key0 = k_lo + j * kN;
-            ok = mbar_wait(&s_full[grp], parity);
-            if (!ok && lane == 0) { atomicExch(error_flag, 15); s_abort = 1; }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
-            if (!ok) break;
+            bool good = mbar_wait(&s_full[B], (uint32_t)(done & 1));
+            if (!good && lane == 0) { atomicExch(error_flag, 15); s_abort = 1; }
+            good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
+            if (!good) return false;
             tcgen05_fence_after();
             const bool need_mask = key0 + kN - 1 > pos || window > 0;
             const int hi = pos - key0;                              // columns <= hi are visible ...
             const int lo = window > 0 ? hi - window : -1;           // ... and > lo
-            // this thread's 64 scores, read from tensor memory once; masked ones become -inf here, so that the
+            // this thread's 32 scores, read from tensor memory once; masked ones become -inf here, so that the
             // maximum (the scale is positive: applied afterwards) and the exponentials need no second look at the mask
-            uint32_t v[64];
-            tmem_ld_32x32b_x32(lane_addr + s_col + (uint32_t)cb, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-            tmem_ld_32x32b_x32(lane_addr + s_col + (uint32_t)(cb + 32), *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(lane_addr + s_col + (uint32_t)cb, v);
             tmem_ld_wait();
             float mx = -INFINITY;
             if (need_mask) {
 #pragma unroll
-                for (int e = 0; e < 64; ++e) {
+                for (int e = 0; e < 32; ++e) {
                     const int col = cb + e;
                     if (!(col <= hi && col > lo)) v[e] = __float_as_uint(-INFINITY);
                 }
             }
 #pragma unroll
-            for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-            s_mx[grp][done & 1][half][row_local] = mx;
-            pair_barrier();                         // both threads of the row hold their scores in registers from here on
-            mx = fmaxf(s_mx[grp][done & 1][0][row_local], s_mx[grp][done & 1][1][row_local]) * scale_log2;
-            // raise the reference maximum only when it would grow by more than 8 (values stay below 2^8); both
+            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+            s_mx[B][cq][row_local] = mx;
+            row_barrier();                          // all four threads of the row hold their scores in registers from here on
+            mx = fmaxf(fmaxf(s_mx[B][0][row_local], s_mx[B][1][row_local]), fmaxf(s_mx[B][2][row_local], s_mx[B][3][row_local])) * scale_log2;
+            // raise the reference maximum only when it would grow by more than 8 (values stay below 2^8); the
             // threads of a row see the same numbers and decide alike
             float corr = 1.f;
             bool rescale = false;
@@ -377,9 +387,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             }
             // P = 2^(s * scale - m): one fused multiply-add and one ex2 per score, packed two to a register
             const float m_eff = m_used == -INFINITY ? 0.f : m_used;
-            uint32_t p[32];
+            uint32_t p[16];
 #pragma unroll
-            for (int e = 0; e < 64; e += 2) {
+            for (int e = 0; e < 32; e += 2) {
                 float pe[2];
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
@@ -390,56 +400,64 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                 __nv_bfloat162 pk = __floats2bfloat162_rn(pe[0], pe[1]);
                 p[e / 2] = *reinterpret_cast<uint32_t*>(&pk);
             }
-            // the group's O is only touched once P V of its tile before has finished
+            // the set's O is only touched once P V of its tile before has finished
             if (done > 0 && __any_sync(0xffffffffu, rescale)) {
-                ok = mbar_wait(&pv_done[grp], (uint32_t)((done - 1) & 1));
-                if (!ok && lane == 0) { atomicExch(error_flag, 16); s_abort = 1; }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
+                good = mbar_wait(&pv_done[B], (uint32_t)((done - 1) & 1));
+                if (!good && lane == 0) { atomicExch(error_flag, 16); s_abort = 1; }
+                good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0;
+                if (!good) return false;
                 tcgen05_fence_after();
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t o[32];
-                    tmem_ld_32x32b_x32(lane_addr + o_col + (uint32_t)(cb + c * 32), o);
-                    tmem_ld_wait();
+                uint32_t o[32];
+                tmem_ld_32x32b_x32(lane_addr + o_col + (uint32_t)cb, o);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * (rescale ? corr : 1.f));
-                    tst32(lane_addr + o_col + (uint32_t)(cb + c * 32), o);
-                }
+                for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * (rescale ? corr : 1.f));
+                tst32(lane_addr + o_col + (uint32_t)cb, o);
             }
-            // P: this thread's 64 keys are 32 columns behind the 32 of the row's other thread, over the scores that
-            // both threads hold in registers since the barrier above
-            tst32(lane_addr + s_col + (uint32_t)(half * 32), p);
+            // P (bfloat16, two keys to a column): this thread's 32 keys take the columns 16 cq .. + 15, over scores
+            // that the row's threads hold in registers since the barrier above
+            tst16(lane_addr + s_col + (uint32_t)(cq * 16), p);
             tst_wait();
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_ready[grp]);
+            if (lane == 0) mbar_arrive(&p_ready[B]);
+            return true;
+        };
+        for (int j = 0; j < num_tiles && ok; j += 2) {
+            ok = softmax_tile(j, std::integral_constant<int, 0>{});
+            if (ok && j + 1 < num_tiles) ok = softmax_tile(j + 1, std::integral_constant<int, 1>{});
         }
-        // ---- merge the two groups: O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)) ----
-        if (ok && done > 0) {
-            ok = mbar_wait(&pv_done[grp], (uint32_t)((done - 1) & 1));
-            if (!ok && lane == 0) { atomicExch(error_flag, 17); s_abort = 1; }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        // ---- merge the two sets: O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)) ----
+        // every thread waits for the last P V of both sets itself: behind them no MMA reads shared or tensor memory
+#pragma unroll
+        for (int B = 0; B < 2; ++B) {
+            if (ok && num_tiles > B) {
+                const int last = ((num_tiles - 1 - B) >> 1);        // the set's last tile is its (last + 1)-th
+                ok = mbar_wait(&pv_done[B], (uint32_t)(last & 1));
+                if (!ok && lane == 0) { atomicExch(error_flag, 17); s_abort = 1; }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
         }
-        s_l[grp][half][row_local] = l;
-        if (half == 0) s_m[grp][row_local] = m_used;
+        s_l[0][cq][row_local] = l_set[0];
+        s_l[1][cq][row_local] = l_set[1];
         tcgen05_fence_before();
-        asm volatile("bar.sync 9, %0;" ::"r"(kMmaWarp * 32) : "memory");      // the sixteen softmax warps
+        row_barrier();                  // the four threads of a row
         tcgen05_fence_after();
         if (!(*(volatile int*)&s_abort) && num_tiles > 0) {
-            // group grp stores the output columns 32 grp .. + 31 of this thread's half of the head
-            const float m0 = s_m[0][row_local], m1 = s_m[1][row_local];
-            const float l0 = s_l[0][0][row_local] + s_l[0][1][row_local], l1 = s_l[1][0][row_local] + s_l[1][1][row_local];
+            // this thread stores the output columns 32 cq .. + 31 of its row
+            const float m0 = m_set[0], m1 = m_set[1];
+            const float l0 = (s_l[0][0][row_local] + s_l[0][1][row_local]) + (s_l[0][2][row_local] + s_l[0][3][row_local]);
+            const float l1 = (s_l[1][0][row_local] + s_l[1][1][row_local]) + (s_l[1][2][row_local] + s_l[1][3][row_local]);
             const float m = fmaxf(m0, m1);
             const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - m);
             const float total = l0 * w0 + l1 * w1;
             // (total is at least 2^-8 for a row with a visible key and at most a few thousand)
             const float inv = total > 0.f ? __fdividef(1.f, total) : 0.f;
             const float f0 = w0 * inv, f1 = w1 * inv;
-            const bool has1 = num_tiles > 1;        // group 1 has an accumulator only if there was a second tile
+            const bool has1 = num_tiles > 1;        // set 1 has an accumulator only if there was a second tile
             uint32_t a[32], b[32];
-            tmem_ld_32x32b_x32(lane_addr + (uint32_t)(2 * kN + cb + grp * 32), a);
-            if (has1) tmem_ld_32x32b_x32(lane_addr + (uint32_t)(3 * kN + cb + grp * 32), b);
+            tmem_ld_32x32b_x32(lane_addr + (uint32_t)(2 * kN + cb), a);
+            if (has1) tmem_ld_32x32b_x32(lane_addr + (uint32_t)(3 * kN + cb), b);
             tmem_ld_wait();
             // into the query tile's shared memory (every S has read it), a row's 256 bytes together, its 16-byte pieces
             // swapped by the row number so that neither these stores nor the loads below meet in a bank
@@ -456,7 +474,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                 __nv_bfloat162 t2 = __floats2bfloat162_rn(y[4], y[5]), t3 = __floats2bfloat162_rn(y[6], y[7]);
                 pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
                 pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
-                const int piece = (cb + grp * 32 + e) >> 3;
+                const int piece = (cb + e) >> 3;
                 *reinterpret_cast<uint4*>(sQ + row_local * 256 + ((piece ^ (row_local & 15)) << 4)) = pk;
             }
         }
