@@ -510,6 +510,35 @@ def test_attention_tcgen05(nq, nkv, ps, window):
     assert not k.attention_tcgen05_supports(128, 8, 8, 5) and not k.attention_tcgen05_supports(128, 8, 8, 4)
 
 
+@pytest.mark.parametrize("seed", [1, 2])
+def test_attention_tcgen05_random_batches(seed):
+    """Drawn batches: 1 to 70 requests (more than the 32 that one pass of the request search takes), portions of 1 to
+    513 tokens after 0 to 1 100 cached ones, every page size and ratio of heads the kernel takes, with and without a
+    window, the same launch three times over."""
+    k = _k()
+    d = 128
+    rnd = random.Random(seed)
+    for it in range(8):
+        nq, nkv = rnd.choice([(16, 8), (32, 8), (8, 8), (16, 2), (32, 2), (4, 1), (64, 8)])
+        ps = rnd.choice([8, 16, 32, 64, 128, 256])
+        requests = rnd.choice([1, 2, 3, 5, 9, 33, 40, 70])
+        new = [rnd.choice([1, 1, 2, 3, 17, 63, 64, 65, 127, 128, 129, 200, 300, 513]) for _ in range(requests)]
+        if requests > 20:
+            new = [min(n, 70) for n in new]
+        lens = [n + rnd.choice([0, 0, 1, 15, 16, 100, 127, 128, 500, 1100]) for n in new]
+        window = rnd.choice([None, None, None, 1, 5, 64, 128, 300])
+        assert k.attention_tcgen05_supports(d, nq, nkv, ps)
+        case = attention_case(torch.bfloat16, nq, nkv, d, lens, new, ps, seed=1000 * seed + it, sharp=rnd.random() < 0.5, poison=True)
+        scale = 1.0 / math.sqrt(d)
+        out = torch.full((sum(new), nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        wide, cache, bt = case["wide"].to(DEV), case["cache"].to(DEV), case["bt"].to(DEV)
+        for _ in range(3):
+            k.attention_tcgen05(wide, out, cache, bt, i32(case["qsl"]), i32(lens), new, nq, nkv, d, scale, window or 0)
+        k.check_error_flags()
+        close(out, attention_reference(case, lens, new, scale, window), 1.5e-2)
+
+
 @pytest.mark.parametrize("requests", [3, 45])
 @pytest.mark.parametrize("splits", [2, 4])
 def test_paged_attention_decode_cluster_and_memory_combine(requests, splits):
