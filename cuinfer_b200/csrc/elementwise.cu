@@ -107,8 +107,14 @@ template <typename TD, typename TO, int CH>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ delta, AnyVec weight, float eps,
                         TO* __restrict__ out, int hidden, int rows) {
+    // the gains do not come from the kernel before this one: they are in shared memory before the dependency wait,
+    // instead of a trip to the L2 after the reduction
+    __shared__ __align__(16) float s_gain[CH * 128];
     griddep_launch();
+    if (out)
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) s_gain[i] = weight[i];
     griddep_wait();          // residual and delta come from the kernels before this one
+    __syncthreads();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= rows) return;
@@ -150,7 +156,7 @@ add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ del
         if (i < hidden) {
             float y[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) y[k] = x[c][k] * factor * weight[i + k];
+            for (int k = 0; k < 4; ++k) y[k] = x[c][k] * factor * s_gain[i + k];
             Vec<TO, 4>::store(out + row + i, y);
         }
     }
