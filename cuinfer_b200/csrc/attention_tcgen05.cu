@@ -352,7 +352,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             bool good = mbar_wait(&s_full[B], (uint32_t)(done & 1));
             if (!good && lane == 0) { atomicExch(error_flag, 15); s_abort = 1; }
             good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0 && !(*(volatile int*)&s_abort);
-            if (!good) return false;
+            if (!good) {
+                row_barrier();      // a warp that gives up still meets the row's other warps at every barrier they reach
+                return false;
+            }
             tcgen05_fence_after();
             const bool need_mask = key0 + kN - 1 > pos || window > 0;
             const int hi = pos - key0;                              // columns <= hi are visible ...
@@ -423,9 +426,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             if (lane == 0) mbar_arrive(&p_ready[B]);
             return true;
         };
-        for (int j = 0; j < num_tiles && ok; j += 2) {
-            ok = softmax_tile(j, std::integral_constant<int, 0>{});
-            if (ok && j + 1 < num_tiles) ok = softmax_tile(j + 1, std::integral_constant<int, 1>{});
+        for (int j = 0; j < num_tiles; j += 2) {
+            // after a wait has run out (never in a healthy run) only the tiles' barriers are kept, so that no warp of
+            // the row is left waiting at one
+            if (ok) ok = softmax_tile(j, std::integral_constant<int, 0>{});
+            else row_barrier();
+            if (j + 1 < num_tiles) {
+                if (ok) ok = softmax_tile(j + 1, std::integral_constant<int, 1>{});
+                else row_barrier();
+            }
         }
         // ---- merge the two sets: O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)) ----
         // every thread waits for the last P V of both sets itself: behind them no MMA reads shared or tensor memory
